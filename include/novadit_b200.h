@@ -1,0 +1,180 @@
+/*
+ * novadit_b200 — C ABI of the B200 (sm_100a) DiT operator kernels.
+ *
+ * Plain pointers and sizes only: no torch types, no exceptions, no allocation,
+ * no synchronisation. Every entry point validates its arguments, enqueues its
+ * kernels on `stream` (a cudaStream_t passed as void*; NULL = the legacy
+ * default stream) of the CURRENT device and returns ND_OK or a negative
+ * nd_status. All pointers are device pointers on that device unless stated.
+ *
+ * Row sharding: the row operators see `rows` consecutive rows of the
+ * flattened [B*S, H] activation starting at global row `row_start`; sample
+ * index b = (row_start + r) / seq_len selects the modulation vector, so
+ * `scale` / `shift` / `dscale` / `dshift` always point at the FULL [B, H]
+ * arrays while x / y / dy / dx / statistics point at the local shard.
+ *
+ * Each declaration cites the interface of the NovaDiT reference it replaces
+ * (path inside that project : line).
+ */
+#ifndef NOVADIT_B200_H_
+#define NOVADIT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+enum {
+  ND_OK = 0,
+  ND_ERR_BAD_ARG = -1,     /* null pointer, negative size, inconsistent shape */
+  ND_ERR_UNSUPPORTED = -2, /* dtype / size outside what the kernels cover */
+  ND_ERR_LAUNCH = -3,      /* CUDA reported an error at launch; see nd_last_cuda_error() */
+  ND_ERR_WORKSPACE = -4,   /* workspace missing, too small or misaligned */
+  ND_ERR_DEVICE = -5       /* a bounded device-side wait expired (see the status argument of nd_fc1_fwd) */
+};
+
+/* element types. csrc/common/type_dispatch.h:5-6 dispatches on the same set */
+enum { ND_F16 = 0, ND_BF16 = 1, ND_F32 = 2, ND_E4M3 = 3 };
+
+/* activation ids: csrc/common/dispatch.h:7-10 (kSilu = 0, kGelu = 1; GELU is the tanh form) */
+enum { ND_ACT_SILU = 0, ND_ACT_GELU = 1 };
+
+const char* nd_status_string(int status);
+/* cudaError_t of the last failed launch on the calling thread (0 if none) */
+int nd_last_cuda_error(void);
+int nd_version(void);
+
+/* Tuning hook: force the row-tile height of the norm kernels (0 = built-in choice). Process-wide;
+ * affects nd_norm_dparam_ws_bytes. No counterpart in the reference. */
+void nd_tune_norm_tile_rows(int tile_rows);
+
+/* ------------------------------------------------------------------ AdaLN */
+
+/* y = LN(x) * (1 + scale[b]) + shift[b]; writes fp32 mean / invstd per row when
+ * both pointers are non-null (training) and skips them when both are null
+ * (inference). dtype: ND_F16, ND_BF16 or ND_F32 (x, scale, shift, y share it).
+ * Replaces fused_adaln_{fp16,bf16}_ungated_forward and the inference variants,
+ * csrc/ops/adaln_kernel.cu:960-1020, called from fused_adaln_forward :1022-1073
+ * and fused_adaln_forward_inference :1075-1145. */
+int nd_adaln_fwd(int dtype, const void* x, const void* scale, const void* shift, void* y,
+                 float* mean, float* invstd, int64_t rows, int64_t row_start, int64_t seq_len,
+                 int64_t hidden, float eps, void* stream);
+
+/* dx = invstd * (dxhat - mean_h(dxhat) - xhat * mean_h(dxhat * xhat)), dxhat = dy * (1 + scale[b]).
+ * Replaces the launcher behind fused_adaln_backward_dx, csrc/ops/adaln_kernel.cu:1147-1193
+ * (kernel :473-582). */
+int nd_adaln_bwd_dx(int dtype, const void* dy, const void* x, const void* scale,
+                    const float* mean, const float* invstd, void* dx, int64_t rows,
+                    int64_t row_start, int64_t seq_len, int64_t hidden, void* stream);
+
+/* Bytes of scratch the dparam / fused backward entry points need for this shard
+ * (0 when a single row tile covers each sample). The first
+ * nd_norm_dparam_ws_counter_bytes() bytes hold per-sample arrival counters that
+ * must be ZERO before the first use; the kernels leave them zero again, so one
+ * cudaMemset after allocation is enough (or call nd_norm_dparam_ws_init). The
+ * base must be 256-byte aligned. One workspace serves one launch at a time. */
+size_t nd_norm_dparam_ws_bytes(int64_t rows, int64_t row_start, int64_t seq_len, int64_t hidden);
+size_t nd_norm_dparam_ws_counter_bytes(int64_t rows, int64_t row_start, int64_t seq_len,
+                                       int64_t hidden);
+int nd_norm_dparam_ws_init(void* ws, size_t ws_bytes, int64_t rows, int64_t row_start,
+                           int64_t seq_len, int64_t hidden, void* stream);
+
+/* dscale[b,h] = sum_s dy * xhat, dshift[b,h] = sum_s dy over the shard's rows of
+ * sample b, fp32, for every sample the shard touches (other rows of dscale /
+ * dshift are left untouched). Two-stage and deterministic: fp32 partials per
+ * row tile in `ws`, then a fixed-order sum by the tile that finishes last.
+ * Replaces the launcher behind fused_adaln_backward_dparam,
+ * csrc/ops/adaln_kernel.cu:1195-1245 (kernel :584-615). */
+int nd_adaln_bwd_dparam(int dtype, const void* dy, const void* x, const float* mean,
+                        const float* invstd, float* dscale, float* dshift, int64_t rows,
+                        int64_t row_start, int64_t seq_len, int64_t hidden, void* ws,
+                        size_t ws_bytes, void* stream);
+
+/* dx and dscale/dshift in ONE pass over dy and x (what the autograd backward of
+ * novadit/ops/adaln.py:25-47 needs when every input wants a gradient; the
+ * reference launches the two kernels above one after the other). */
+int nd_adaln_bwd(int dtype, const void* dy, const void* x, const void* scale, const float* mean,
+                 const float* invstd, void* dx, float* dscale, float* dshift, int64_t rows,
+                 int64_t row_start, int64_t seq_len, int64_t hidden, void* ws, size_t ws_bytes,
+                 void* stream);
+
+/* ------------------------------------------------------------- AdaRMSNorm */
+
+/* y = x * inv_rms * (1 + scale[b]) + shift[b], inv_rms = 1/sqrt(mean(x^2) + eps);
+ * inv_rms nullable (inference). Replaces fused_adarmsnorm_{fp16,bf16}_forward,
+ * csrc/ops/adarmsnorm_kernel.cu:928-961 (entry points :965-1060). */
+int nd_adarms_fwd(int dtype, const void* x, const void* scale, const void* shift, void* y,
+                  float* inv_rms, int64_t rows, int64_t row_start, int64_t seq_len,
+                  int64_t hidden, float eps, void* stream);
+
+/* dx = inv_rms * (dxhat - xhat * mean_h(dxhat * xhat)). Replaces
+ * fused_adarmsnorm_backward_dx, csrc/ops/adarmsnorm_kernel.cu:457-565. */
+int nd_adarms_bwd_dx(int dtype, const void* dy, const void* x, const void* scale,
+                     const float* inv_rms, void* dx, int64_t rows, int64_t row_start,
+                     int64_t seq_len, int64_t hidden, void* stream);
+
+/* Replaces fused_adarmsnorm_backward_dparam, csrc/ops/adarmsnorm_kernel.cu:571-600. */
+int nd_adarms_bwd_dparam(int dtype, const void* dy, const void* x, const float* inv_rms,
+                         float* dscale, float* dshift, int64_t rows, int64_t row_start,
+                         int64_t seq_len, int64_t hidden, void* ws, size_t ws_bytes,
+                         void* stream);
+
+/* One-pass dx + dscale/dshift (autograd backward of novadit/ops/adarmsnorm.py:25-47). */
+int nd_adarms_bwd(int dtype, const void* dy, const void* x, const void* scale,
+                  const float* inv_rms, void* dx, float* dscale, float* dshift, int64_t rows,
+                  int64_t row_start, int64_t seq_len, int64_t hidden, void* ws, size_t ws_bytes,
+                  void* stream);
+
+/* --------------------------------------------------------------- gate-act */
+
+/* x rows are [up(I) | gate(I)]; y = up * act(gate). dtype ND_F16 / ND_BF16 / ND_F32.
+ * Replaces fused_gate_act_{fp32,fp16,bf16}_forward, csrc/ops/gate_act_kernel.cu:536-600
+ * (entry points fused_gate_act_forward / fused_geglu_forward :604-721). */
+int nd_gate_act_fwd(int dtype, int act, const void* x, void* y, int64_t rows, int64_t inter,
+                    void* stream);
+
+/* dz = [dy * act(gate) | dy * up * act'(gate)], rows of 2I. Replaces the launchers behind
+ * fused_gate_act_backward / fused_geglu_backward, csrc/ops/gate_act_kernel.cu:723-857. */
+int nd_gate_act_bwd(int dtype, int act, const void* dy, const void* x, void* dz, int64_t rows,
+                    int64_t inter, void* stream);
+
+/* -------------------------------------------------------------------- FC1 */
+
+/* z = (x @ w^T) * alpha + bias, x [m,k] and w [n,k] both K-contiguous (nn.Linear layout).
+ *   gated == 1: rows [0, n/2) of w (and bias) are the gate, [n/2, n) the value;
+ *               y [m, n/2] = value * act(gate)  (layout of novadit/ops/fc1_bias_act.py:55-68).
+ *   gated == 2: same function, rows interleaved (gate0, value0, gate1, ...): the layout
+ *               fused_fc1_bias_act_forward receives from novadit/ops/fc1_bias_act.py:237-239.
+ *   gated == 0: y [m, n] = act(z).
+ * ab_dtype: ND_BF16, ND_F16 or ND_E4M3 (both operands); out_dtype: ND_BF16 or ND_F16, also the
+ * dtype of `bias` (nullable, length n). alpha = alpha_host * (alpha_dev ? alpha_dev[0] *
+ * alpha_dev[1] : 1): pass the two per-tensor de-quantisation scales of an FP8 call as a
+ * 2-float device array so no host round trip is needed. fp32 accumulation in tensor memory.
+ * Needs k % 16 == 0 bytes-aligned rows (k*sizeof(ab) % 16 == 0) and 16-byte aligned bases.
+ * `status` is a device int the kernel sets non-zero if a bounded wait expires (nullable).
+ * Replaces fused_fc1_bias_act_forward, csrc/ops/fc1_bias_act_kernel.cu:54-72 (a stub that
+ * raises), and the launch of the CuTe-DSL kernel, novadit/ops/fc1_bias_act.py:227-235 with
+ * csrc/cute_dsl/fc1_bias_act/aot_bridge.h:17-37 as the intended C signature. */
+int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const void* x, const void* w,
+               const void* bias, float alpha_host, const float* alpha_dev, void* y, int64_t m,
+               int64_t k, int64_t n, int* status, void* stream);
+
+/* amax = max |x| over n elements (fp32 result, device). Two-stage and deterministic:
+ * `ws` holds per-CTA maxima; nd_amax_ws_bytes() bytes, 256-byte aligned. No counterpart in
+ * the reference (it has no FP8 path). */
+size_t nd_amax_ws_bytes(void);
+int nd_amax(int dtype, const void* x, int64_t n, float* amax, void* ws, size_t ws_bytes,
+            void* stream);
+
+/* q = saturate_e4m3(x * 448 / amax), scale_out[0] = amax / 448 (1 if amax == 0); amax and
+ * scale_out are device floats. No counterpart in the reference. */
+int nd_quant_e4m3(int dtype, const void* x, int64_t n, const float* amax, void* q,
+                  float* scale_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NOVADIT_B200_H_ */

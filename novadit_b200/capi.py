@@ -1,0 +1,270 @@
+"""ctypes binding of the C ABI (`include/novadit_b200.h`) plus tensor-level helpers.
+
+This is the route the parity tests and the benchmark take: torch tensors are
+used only as device buffers (`data_ptr()`), every call goes through the
+`extern "C"` entry points of ``libnovadit_b200.so``. There is no fallback: if the
+library is missing, importing this module's `lib()` raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_int64, c_size_t, c_void_p
+
+import torch
+
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libnovadit_b200.so")
+
+ND_F16, ND_BF16, ND_F32, ND_E4M3 = 0, 1, 2, 3
+ACT_SILU, ACT_GELU = 0, 1
+ACT_IDS = {"silu": ACT_SILU, "gelu": ACT_GELU}
+DTYPE_IDS = {torch.float16: ND_F16, torch.bfloat16: ND_BF16, torch.float32: ND_F32,
+             torch.float8_e4m3fn: ND_E4M3}
+
+_SHAPE4 = [c_int64, c_int64, c_int64, c_int64]  # rows, row_start, seq_len, hidden
+
+# name -> (restype, argtypes); must list every symbol the header declares
+SIGNATURES = {
+    "nd_status_string": (ctypes.c_char_p, [c_int]),
+    "nd_last_cuda_error": (c_int, []),
+    "nd_version": (c_int, []),
+    "nd_tune_norm_tile_rows": (None, [c_int]),
+    "nd_adaln_fwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             *_SHAPE4, c_float, c_void_p]),
+    "nd_adaln_bwd_dx": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                *_SHAPE4, c_void_p]),
+    "nd_norm_dparam_ws_bytes": (c_size_t, _SHAPE4),
+    "nd_norm_dparam_ws_counter_bytes": (c_size_t, _SHAPE4),
+    "nd_norm_dparam_ws_init": (c_int, [c_void_p, c_size_t, *_SHAPE4, c_void_p]),
+    "nd_adaln_bwd_dparam": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_void_p, *_SHAPE4, c_void_p, c_size_t, c_void_p]),
+    "nd_adaln_bwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_void_p, *_SHAPE4, c_void_p, c_size_t, c_void_p]),
+    "nd_adarms_fwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, *_SHAPE4,
+                              c_float, c_void_p]),
+    "nd_adarms_bwd_dx": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, *_SHAPE4,
+                                 c_void_p]),
+    "nd_adarms_bwd_dparam": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     *_SHAPE4, c_void_p, c_size_t, c_void_p]),
+    "nd_adarms_bwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_void_p, *_SHAPE4, c_void_p, c_size_t, c_void_p]),
+    "nd_gate_act_fwd": (c_int, [c_int, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "nd_gate_act_bwd": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                c_void_p]),
+    "nd_fc1_fwd": (c_int, [c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float,
+                           c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "nd_amax_ws_bytes": (c_size_t, []),
+    "nd_amax": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "nd_quant_e4m3": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+}
+
+_lib = None
+
+
+class NovaditError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded C-ABI library. Raises if it has not been built (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise NovaditError(
+                f"{LIB_PATH} is missing: build it with `python -m novadit_b200.build` "
+                "(the operators have no CPU or PyTorch fallback)")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        msg = lib().nd_status_string(status).decode()
+        extra = ""
+        if status == -3:
+            extra = f" (cudaError {lib().nd_last_cuda_error()})"
+        raise NovaditError(f"{what}: {msg}{extra}")
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise NovaditError("tensors must be contiguous CUDA tensors")
+
+
+class Workspace:
+    """A cached, 256-byte aligned device scratch buffer whose leading counter bytes are zero."""
+
+    def __init__(self) -> None:
+        self.buf: torch.Tensor | None = None
+        self.counters_zeroed = 0
+
+    def get(self, nbytes: int, counter_bytes: int, device) -> torch.Tensor | None:
+        if nbytes == 0:
+            return None
+        if self.buf is None or self.buf.numel() < nbytes or self.buf.device != torch.device(device):
+            self.buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            self.counters_zeroed = 0
+        if self.counters_zeroed < counter_bytes:
+            self.buf[:counter_bytes].zero_()
+            self.counters_zeroed = counter_bytes
+        return self.buf
+
+
+_WS = Workspace()
+
+
+# ---------------------------------------------------------------- norm operators
+def norm_fwd(kind, x, scale, shift, eps, *, stats=True, row_start=0, seq_len=None, y=None,
+             mean=None, invstd=None):
+    """AdaLN (`kind="layer"`) / AdaRMSNorm (`kind="rms"`) forward on rows `x` [rows, H] (or [B,S,H]).
+
+    Returns (y, mean, invstd) for "layer" and (y, inv_rms) for "rms"; statistics are None when
+    `stats` is False. `scale`/`shift` are the FULL [B, H] modulation arrays; `row_start` is the
+    global index of x's first row.
+    """
+    _need_cuda(x, scale, shift)
+    hidden = x.shape[-1]
+    if seq_len is None:
+        seq_len = x.shape[1] if x.dim() == 3 else 1
+    rows = x.numel() // hidden
+    y = torch.empty_like(x) if y is None else y
+    lead = x.shape[:-1]
+    dt = DTYPE_IDS[x.dtype]
+    if kind == "layer":
+        if stats:
+            mean = torch.empty(lead, dtype=torch.float32, device=x.device) if mean is None else mean
+            invstd = torch.empty(lead, dtype=torch.float32, device=x.device) if invstd is None else invstd
+        check(lib().nd_adaln_fwd(dt, _ptr(x), _ptr(scale), _ptr(shift), _ptr(y), _ptr(mean), _ptr(invstd),
+                                 rows, row_start, seq_len, hidden, eps, _stream()), "nd_adaln_fwd")
+        return y, mean, invstd
+    if stats:
+        invstd = torch.empty(lead, dtype=torch.float32, device=x.device) if invstd is None else invstd
+    check(lib().nd_adarms_fwd(dt, _ptr(x), _ptr(scale), _ptr(shift), _ptr(y), _ptr(invstd),
+                              rows, row_start, seq_len, hidden, eps, _stream()), "nd_adarms_fwd")
+    return y, invstd
+
+
+def norm_bwd(kind, dy, x, scale, mean, invstd, *, mode="fused", row_start=0, seq_len=None, batch=None,
+             dx=None, dscale=None, dshift=None, ws=None):
+    """Backward. mode: "dx", "dparam" or "fused". Returns (dx, dscale, dshift) with None for parts
+    not computed. dscale/dshift are [batch, H] fp32 over the FULL batch; rows of samples the shard
+    does not touch are left as they were (zero when allocated here)."""
+    _need_cuda(dy, x, scale, mean, invstd)
+    hidden = x.shape[-1]
+    if seq_len is None:
+        seq_len = x.shape[1] if x.dim() == 3 else 1
+    rows = x.numel() // hidden
+    if batch is None:
+        batch = x.shape[0] if x.dim() == 3 else (row_start + rows + seq_len - 1) // seq_len
+    dt = DTYPE_IDS[x.dtype]
+    L = lib()
+    want_dx, want_dp = mode in ("dx", "fused"), mode in ("dparam", "fused")
+    if want_dx and dx is None:
+        dx = torch.empty_like(x)
+    ws_t, ws_bytes = None, 0
+    if want_dp:
+        if dscale is None:
+            dscale = torch.zeros(batch, hidden, dtype=torch.float32, device=x.device)
+        if dshift is None:
+            dshift = torch.zeros(batch, hidden, dtype=torch.float32, device=x.device)
+        ws_bytes = L.nd_norm_dparam_ws_bytes(rows, row_start, seq_len, hidden)
+        cnt = L.nd_norm_dparam_ws_counter_bytes(rows, row_start, seq_len, hidden)
+        ws_t = (ws or _WS).get(ws_bytes, cnt, x.device)
+    st = _stream()
+    shape = (rows, row_start, seq_len, hidden)
+    if kind == "layer":
+        if mode == "dx":
+            check(L.nd_adaln_bwd_dx(dt, _ptr(dy), _ptr(x), _ptr(scale), _ptr(mean), _ptr(invstd), _ptr(dx),
+                                    *shape, st), "nd_adaln_bwd_dx")
+        elif mode == "dparam":
+            check(L.nd_adaln_bwd_dparam(dt, _ptr(dy), _ptr(x), _ptr(mean), _ptr(invstd), _ptr(dscale),
+                                        _ptr(dshift), *shape, _ptr(ws_t), ws_bytes, st), "nd_adaln_bwd_dparam")
+        else:
+            check(L.nd_adaln_bwd(dt, _ptr(dy), _ptr(x), _ptr(scale), _ptr(mean), _ptr(invstd), _ptr(dx),
+                                 _ptr(dscale), _ptr(dshift), *shape, _ptr(ws_t), ws_bytes, st), "nd_adaln_bwd")
+    else:
+        if mode == "dx":
+            check(L.nd_adarms_bwd_dx(dt, _ptr(dy), _ptr(x), _ptr(scale), _ptr(invstd), _ptr(dx), *shape, st),
+                  "nd_adarms_bwd_dx")
+        elif mode == "dparam":
+            check(L.nd_adarms_bwd_dparam(dt, _ptr(dy), _ptr(x), _ptr(invstd), _ptr(dscale), _ptr(dshift),
+                                         *shape, _ptr(ws_t), ws_bytes, st), "nd_adarms_bwd_dparam")
+        else:
+            check(L.nd_adarms_bwd(dt, _ptr(dy), _ptr(x), _ptr(scale), _ptr(invstd), _ptr(dx), _ptr(dscale),
+                                  _ptr(dshift), *shape, _ptr(ws_t), ws_bytes, st), "nd_adarms_bwd")
+    return dx, dscale, dshift
+
+
+# ---------------------------------------------------------------- gate-act
+def gate_act_fwd(x, act="silu", y=None):
+    _need_cuda(x)
+    inter = x.shape[-1] // 2
+    rows = x.numel() // (2 * inter)
+    y = torch.empty(*x.shape[:-1], inter, dtype=x.dtype, device=x.device) if y is None else y
+    check(lib().nd_gate_act_fwd(DTYPE_IDS[x.dtype], ACT_IDS[act], _ptr(x), _ptr(y), rows, inter, _stream()),
+          "nd_gate_act_fwd")
+    return y
+
+
+def gate_act_bwd(dy, x, act="silu", dz=None):
+    _need_cuda(dy, x)
+    inter = x.shape[-1] // 2
+    rows = x.numel() // (2 * inter)
+    dz = torch.empty_like(x) if dz is None else dz
+    check(lib().nd_gate_act_bwd(DTYPE_IDS[x.dtype], ACT_IDS[act], _ptr(dy), _ptr(x), _ptr(dz), rows, inter,
+                                _stream()), "nd_gate_act_bwd")
+    return dz
+
+
+# ---------------------------------------------------------------- FC1
+def fc1_fwd(x, w, bias=None, act="silu", gated=True, *, alpha=1.0, alpha_dev=None, out_dtype=None, y=None,
+            status=None):
+    """x [..., K], w [N, K] -> y [..., N/2] (gated) or [..., N]. Operands bf16/fp16/e4m3."""
+    _need_cuda(x, w, bias)
+    k = x.shape[-1]
+    m = x.numel() // k
+    n = w.shape[0]
+    if out_dtype is None:
+        out_dtype = torch.bfloat16 if x.dtype == torch.float8_e4m3fn else x.dtype
+    n_out = n // 2 if gated else n
+    if y is None:
+        y = torch.empty(*x.shape[:-1], n_out, dtype=out_dtype, device=x.device)
+    check(lib().nd_fc1_fwd(DTYPE_IDS[x.dtype], DTYPE_IDS[out_dtype], ACT_IDS[act], int(gated), _ptr(x), _ptr(w),
+                           _ptr(bias), float(alpha), _ptr(alpha_dev), _ptr(y), m, k, n, _ptr(status), _stream()),
+          "nd_fc1_fwd")
+    return y
+
+
+_AMAX_WS: dict = {}
+
+
+def quantize_e4m3(x):
+    """Per-tensor amax scaling to e4m3 on the device. Returns (q, scale[1] fp32 device tensor)."""
+    _need_cuda(x)
+    L = lib()
+    dev = x.device
+    ws = _AMAX_WS.get(dev)
+    if ws is None:
+        ws = _AMAX_WS[dev] = torch.empty(L.nd_amax_ws_bytes(), dtype=torch.uint8, device=dev)
+    amax = torch.empty(1, dtype=torch.float32, device=dev)
+    scale = torch.empty(1, dtype=torch.float32, device=dev)
+    q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=dev)
+    st = _stream()
+    check(L.nd_amax(DTYPE_IDS[x.dtype], _ptr(x), x.numel(), _ptr(amax), _ptr(ws), ws.numel(), st), "nd_amax")
+    check(L.nd_quant_e4m3(DTYPE_IDS[x.dtype], _ptr(x), x.numel(), _ptr(amax), _ptr(q), _ptr(scale), st),
+          "nd_quant_e4m3")
+    return q, scale

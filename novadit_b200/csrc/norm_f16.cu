@@ -1,0 +1,6 @@
+// AdaLN / AdaRMSNorm kernels instantiated for __half rows.
+#include "norm_impl.cuh"
+
+namespace nd {
+int launch_norm_f16(const NormArgs& a, cudaStream_t st) { return launch_norm<__half>(a, st); }
+}  // namespace nd

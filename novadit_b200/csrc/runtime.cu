@@ -1,0 +1,49 @@
+// Process-wide helpers of the C ABI: status strings, last CUDA error, device facts.
+#include "common.cuh"
+
+namespace nd {
+
+static thread_local int t_last_cuda_error = 0;
+
+void set_last_cuda_error(cudaError_t e) { t_last_cuda_error = static_cast<int>(e); }
+
+int sm_count() {
+  constexpr int kMaxDevices = 64;
+  static int cache[kMaxDevices] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    (void)cudaGetLastError();
+    return 148;
+  }
+  if (cache[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = 148;
+    }
+    cache[dev] = n;
+  }
+  return cache[dev];
+}
+
+}  // namespace nd
+
+extern "C" {
+
+const char* nd_status_string(int status) {
+  switch (status) {
+    case ND_OK: return "ok";
+    case ND_ERR_BAD_ARG: return "bad argument (null pointer, negative size or inconsistent shape)";
+    case ND_ERR_UNSUPPORTED: return "unsupported element type or size";
+    case ND_ERR_LAUNCH: return "CUDA launch failed";
+    case ND_ERR_WORKSPACE: return "workspace missing, too small or not 256-byte aligned";
+    case ND_ERR_DEVICE: return "a bounded device-side wait expired";
+    default: return "unknown status";
+  }
+}
+
+int nd_last_cuda_error(void) { return nd::t_last_cuda_error; }
+
+int nd_version(void) { return 100; }
+
+}  // extern "C"

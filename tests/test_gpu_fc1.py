@@ -1,0 +1,128 @@
+"""Fused FC1 (tcgen05) against the CPU oracle and the reference's golden vectors, through the C ABI."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import novadit_b200.ops as ops
+from novadit_b200 import capi, synth
+from oracle import novadit_oracle as oracle
+from tests import golden_io
+from tests.helpers import FP8_REL_L2, assert_half_parity
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+FC1 = golden_io.load("fc1_golden")
+
+
+def new_status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def run(x, w, b, act, layout, **kw):
+    """layout: 1 = stacked [gate | value] rows, 2 = interleaved rows, 0 = no gating."""
+    status = new_status()
+    wd = w.to(DEV)
+    bd = None if b is None else b.to(DEV)
+    if layout == 2:
+        wd = ops.interleave_weight(wd)
+        bd = None if bd is None else ops.interleave_bias(bd)
+    y = capi.fc1_fwd(x.to(DEV), wd, bd, act, layout, status=status, **kw)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, f"device-side wait expired, code {int(status.item())}"
+    return y
+
+
+@pytest.mark.parametrize("case", sorted(FC1))
+def test_matches_reference_golden_vectors(case):
+    g = FC1[case]
+    dtype = golden_io.DTYPES[g["dtype"]]
+    m, k, n = (int(v) for v in g["shape"])
+    x, w, b = synth.fc1_inputs(m, k, n, dtype, int(g["seed"]))
+    y = run(x, w, b if g["with_bias"] else None, g["act"], 1)
+    assert_half_parity(y, golden_io.unpack(g["y"], dtype).reshape(m, n // 2), case)
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+@pytest.mark.parametrize("layout", [0, 1, 2])
+@pytest.mark.parametrize("dtype,mkn,bias", [
+    (torch.bfloat16, (64, 128, 128), True),      # the reference's JIT numeric test shape (M=64, H=128, I=64)
+    (torch.float16, (64, 128, 128), False),
+    (torch.bfloat16, (256, 768, 1536), True),    # DiT-S like, several k-blocks and n-tiles
+    (torch.bfloat16, (300, 200, 272), True),     # ragged M, K and N tiles (zero-filled tails)
+    (torch.float16, (129, 1152, 528), True),
+    (torch.bfloat16, (1, 64, 16), True),         # a single row
+])
+def test_matches_oracle(act, layout, dtype, mkn, bias):
+    m, k, n = mkn
+    x, w, b = synth.fc1_inputs(m, k, n, dtype, seed=50 + m % 7)
+    y = run(x, w, b if bias else None, act, layout)
+    want = oracle.fc1_fwd(x, w, b if bias else None, act, gated=layout != 0, compute=torch.float64)
+    assert_half_parity(y, want, f"fc1 {act} layout {layout} {dtype} {mkn}")
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+def test_config4_bf16(layout):
+    """Workload config 4: M=8192, K=1152, N=4608, bias, GELU-tanh, bf16 (gated as in the reference, and plain)."""
+    x, w, b = synth.fc1_inputs(8192, 1152, 4608, torch.bfloat16, seed=0)
+    y = run(x, w, b, "gelu", layout)
+    want = oracle.fc1_fwd(x, w, b, "gelu", gated=layout != 0)
+    assert_half_parity(y, want, f"config4 layout {layout}")
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+def test_config4_fp8_e4m3(layout):
+    """FP8 e4m3 operands with per-tensor amax scales; bar: relative L2 <= 3e-2 against the fp32 GEMM of the
+    de-quantised operands. The quantisation itself must match the oracle's bit for bit."""
+    x, w, b = synth.fc1_inputs(8192, 1152, 4608, torch.bfloat16, seed=0)
+    qx, sx = capi.quantize_e4m3(x.to(DEV))
+    qw, sw = capi.quantize_e4m3(w.to(DEV))
+    oqx, osx = oracle.quant_e4m3(x)
+    oqw, osw = oracle.quant_e4m3(w)
+    assert abs(float(sx) - osx) <= 1e-6 * osx and abs(float(sw) - osw) <= 1e-6 * osw
+    assert torch.equal(qx.cpu().view(torch.uint8), oqx.view(torch.uint8))
+    assert torch.equal(qw.cpu().view(torch.uint8), oqw.view(torch.uint8))
+    status = new_status()
+    y = capi.fc1_fwd(qx, qw, b.to(DEV), "gelu", layout, alpha_dev=torch.cat([sx, sw]), out_dtype=torch.bfloat16,
+                     status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    want = oracle.fc1_fwd_fp8(oqx, osx, oqw, osw, b, "gelu", gated=layout != 0)
+    rl = oracle.rel_l2(y.cpu(), want)
+    assert rl <= FP8_REL_L2, f"fp8 rel_l2 {rl:.3e}"
+    assert rl <= 5e-3, f"fp8 kernel error vs de-quantised fp32 GEMM unexpectedly large: {rl:.3e}"
+    # information: distance to the un-quantised product (dominated by quantisation, not by the kernel)
+    print("fp8 vs unquantised fp32:", oracle.rel_l2(y.cpu(), oracle.fc1_fwd(x, w, b, "gelu", gated=layout != 0)))
+
+
+def test_large_case_properties():
+    """M=32768, K=3072, N=12288: sampled rows against an fp32 GEMM and row independence."""
+    m, k, n = 32768, 3072, 12288
+    g = torch.Generator(device=DEV).manual_seed(21)
+    x = torch.randn(m, k, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g, device=DEV) * 0.02).to(torch.bfloat16)
+    b = (torch.randn(n, generator=g, device=DEV) * 0.02).to(torch.bfloat16)
+    status = new_status()
+    y = capi.fc1_fwd(x, w, b, "gelu", 1, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    rows = torch.randint(0, m, (256,), generator=g, device=DEV)
+    xs = x[rows].contiguous()
+    want = oracle.fc1_fwd(xs.cpu(), w.cpu(), b.cpu(), "gelu", gated=True)
+    assert_half_parity(y[rows].cpu(), want, "large case sampled rows")
+    # the same rows computed as their own small problem give the same bits
+    assert torch.equal(capi.fc1_fwd(xs, w, b, "gelu", 1), y[rows])
+
+
+def test_unsupported_shapes_are_rejected_not_mangled():
+    L = capi.lib()
+    x = torch.zeros(8, 20, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(16, 20, dtype=torch.bfloat16, device=DEV)
+    y = torch.zeros(8, 8, dtype=torch.bfloat16, device=DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    # K = 20 bf16 is a 40-byte row pitch: not a multiple of 16 bytes, TMA cannot address it
+    assert L.nd_fc1_fwd(capi.ND_BF16, capi.ND_BF16, 0, 1, x.data_ptr(), w.data_ptr(), None, 1.0, None,
+                        y.data_ptr(), 8, 20, 16, None, st) == -2
+    # n_out = 4 is not a multiple of 8
+    assert L.nd_fc1_fwd(capi.ND_BF16, capi.ND_BF16, 0, 1, x.data_ptr(), w.data_ptr(), None, 1.0, None,
+                        y.data_ptr(), 8, 16, 8, None, st) == -2
