@@ -430,6 +430,39 @@ def run_gpu_arm(args) -> None:
         dist.destroy_process_group()
 
 
+def run_profile_case(op: str, variant: int = -1) -> None:
+    """A handful of direct launches (no graphs, no rotation) of one operator at its benchmark size: the
+    command ncu captures. `op`: norm (config 2 AdaLN fwd + bwd), rms, gate (2048 rows of config 3), fc1."""
+    from novadit_b200 import capi, synth
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    if variant >= 0:
+        capi.lib().nd_tune_norm_variant(variant)
+    if op in ("norm", "rms"):
+        work = NormWorkload("layer" if op == "norm" else "rms", dev)
+        for i in range(6):
+            work.step(work.sets[i % NSETS])
+    elif op == "gate":
+        x, dy = synth.gate_act_inputs(1, 4096, 4608, torch.bfloat16, seed=3)  # 151 MB in + out
+        xg, dyg = x.to(dev), dy.to(dev)
+        for _ in range(3):
+            for act in ("silu", "gelu"):
+                capi.gate_act_fwd(xg, act)
+                capi.gate_act_bwd(dyg, xg, act)
+    elif op == "fc1":
+        xf, wf, bf = (t.to(dev) for t in synth.fc1_inputs(8192, 1152, 4608, torch.bfloat16, seed=0))
+        qx, sx = capi.quantize_e4m3(xf)
+        qw, sw = capi.quantize_e4m3(wf)
+        for _ in range(3):
+            capi.fc1_fwd(xf, wf, bf, "gelu", 1)
+            capi.fc1_fwd(qx, qw, bf, "gelu", 1, alpha_dev=torch.cat([sx, sw]), out_dtype=torch.bfloat16)
+    else:
+        raise SystemExit(f"unknown profile case {op}")
+    torch.cuda.synchronize()
+    print("profile case done:", op)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -438,7 +471,12 @@ def main() -> None:
     ap.add_argument("--impl", default="novadit_b200", choices=["novadit_b200", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the other operators (AdaRMSNorm, gate-act, FC1)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile-variant", type=int, default=-1, help="norm kernel variant for --profile")
+    ap.add_argument("--profile", default=None, help="run a few direct launches of one operator (for ncu) and exit")
     args = ap.parse_args()
+    if args.profile:
+        run_profile_case(args.profile, args.profile_variant)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -46,10 +46,20 @@ const char* nd_status_string(int status);
 /* cudaError_t of the last failed launch on the calling thread (0 if none) */
 int nd_last_cuda_error(void);
 int nd_version(void);
+/* Error word of the current device: 0, or the code a kernel left when one of its bounded waits
+ * (on a bulk copy into shared memory) expired. Synchronises with the device (a blocking copy).
+ * reset != 0 clears it. Negative = nd_status of a failed query. */
+int nd_device_error(int reset);
 
-/* Tuning hook: force the row-tile height of the norm kernels (0 = built-in choice). Process-wide;
- * affects nd_norm_dparam_ws_bytes. No counterpart in the reference. */
+/* Tuning hook: force the row-tile height of the generic norm kernels (0 = built-in choice).
+ * Process-wide; affects nd_norm_dparam_ws_bytes. No counterpart in the reference. */
 void nd_tune_norm_tile_rows(int tile_rows);
+/* Tuning hook: 0 = default (bulk-copy kernels where the row layout allows), 1 = generic kernels for
+ * every shape. Results are identical up to fp32 summation order. No counterpart in the reference. */
+void nd_tune_norm_variant(int variant);
+/* Tuning hook: pipeline depth (shared-memory stages) of the bulk-copy norm kernels; 0 = as many as
+ * fit the per-CTA budget. No counterpart in the reference. */
+void nd_tune_norm_stages(int stages);
 
 /* ------------------------------------------------------------------ AdaLN */
 
@@ -70,22 +80,15 @@ int nd_adaln_bwd_dx(int dtype, const void* dy, const void* x, const void* scale,
                     const float* mean, const float* invstd, void* dx, int64_t rows,
                     int64_t row_start, int64_t seq_len, int64_t hidden, void* stream);
 
-/* Bytes of scratch the dparam / fused backward entry points need for this shard
- * (0 when a single row tile covers each sample). The first
- * nd_norm_dparam_ws_counter_bytes() bytes hold per-sample arrival counters that
- * must be ZERO before the first use; the kernels leave them zero again, so one
- * cudaMemset after allocation is enough (or call nd_norm_dparam_ws_init). The
- * base must be 256-byte aligned. One workspace serves one launch at a time. */
+/* Bytes of scratch the dparam / fused backward entry points need for this shard: fp32 partial
+ * column sums, no counters, nothing to initialise. The base must be 256-byte aligned. One
+ * workspace serves one launch at a time (launches on one stream may share it). */
 size_t nd_norm_dparam_ws_bytes(int64_t rows, int64_t row_start, int64_t seq_len, int64_t hidden);
-size_t nd_norm_dparam_ws_counter_bytes(int64_t rows, int64_t row_start, int64_t seq_len,
-                                       int64_t hidden);
-int nd_norm_dparam_ws_init(void* ws, size_t ws_bytes, int64_t rows, int64_t row_start,
-                           int64_t seq_len, int64_t hidden, void* stream);
 
 /* dscale[b,h] = sum_s dy * xhat, dshift[b,h] = sum_s dy over the shard's rows of
  * sample b, fp32, for every sample the shard touches (other rows of dscale /
  * dshift are left untouched). Two-stage and deterministic: fp32 partials per
- * row tile in `ws`, then a fixed-order sum by the tile that finishes last.
+ * row segment in `ws`, then a second kernel sums them in index order (no atomics).
  * Replaces the launcher behind fused_adaln_backward_dparam,
  * csrc/ops/adaln_kernel.cu:1195-1245 (kernel :584-615). */
 int nd_adaln_bwd_dparam(int dtype, const void* dy, const void* x, const float* mean,

@@ -28,14 +28,15 @@ SIGNATURES = {
     "nd_status_string": (ctypes.c_char_p, [c_int]),
     "nd_last_cuda_error": (c_int, []),
     "nd_version": (c_int, []),
+    "nd_device_error": (c_int, [c_int]),
     "nd_tune_norm_tile_rows": (None, [c_int]),
+    "nd_tune_norm_variant": (None, [c_int]),
+    "nd_tune_norm_stages": (None, [c_int]),
     "nd_adaln_fwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              *_SHAPE4, c_float, c_void_p]),
     "nd_adaln_bwd_dx": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 *_SHAPE4, c_void_p]),
     "nd_norm_dparam_ws_bytes": (c_size_t, _SHAPE4),
-    "nd_norm_dparam_ws_counter_bytes": (c_size_t, _SHAPE4),
-    "nd_norm_dparam_ws_init": (c_int, [c_void_p, c_size_t, *_SHAPE4, c_void_p]),
     "nd_adaln_bwd_dparam": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                     c_void_p, *_SHAPE4, c_void_p, c_size_t, c_void_p]),
     "nd_adaln_bwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -106,21 +107,16 @@ def _need_cuda(*ts: torch.Tensor) -> None:
 
 
 class Workspace:
-    """A cached, 256-byte aligned device scratch buffer whose leading counter bytes are zero."""
+    """A cached, 256-byte aligned device scratch buffer (grown on demand, never initialised)."""
 
     def __init__(self) -> None:
         self.buf: torch.Tensor | None = None
-        self.counters_zeroed = 0
 
-    def get(self, nbytes: int, counter_bytes: int, device) -> torch.Tensor | None:
+    def get(self, nbytes: int, device) -> torch.Tensor | None:
         if nbytes == 0:
             return None
         if self.buf is None or self.buf.numel() < nbytes or self.buf.device != torch.device(device):
             self.buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-            self.counters_zeroed = 0
-        if self.counters_zeroed < counter_bytes:
-            self.buf[:counter_bytes].zero_()
-            self.counters_zeroed = counter_bytes
         return self.buf
 
 
@@ -182,8 +178,7 @@ def norm_bwd(kind, dy, x, scale, mean, invstd, *, mode="fused", row_start=0, seq
         if dshift is None:
             dshift = torch.zeros(batch, hidden, dtype=torch.float32, device=x.device)
         ws_bytes = L.nd_norm_dparam_ws_bytes(rows, row_start, seq_len, hidden)
-        cnt = L.nd_norm_dparam_ws_counter_bytes(rows, row_start, seq_len, hidden)
-        ws_t = (ws or _WS).get(ws_bytes, cnt, x.device)
+        ws_t = (ws or _WS).get(ws_bytes, x.device)
     st = _stream()
     shape = (rows, row_start, seq_len, hidden)
     if kind == "layer":

@@ -25,6 +25,7 @@ inline int check_launch() {
 }
 
 int sm_count();  // multiprocessors of the current device (cached per device)
+int* device_error_ptr();  // device address of the error word kernels set when a bounded wait expires
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -2,7 +2,7 @@
 // plan, workspace layout, dispatch on element type.
 #include <atomic>
 
-#include "norm_impl.cuh"
+#include "norm_launch.cuh"
 
 namespace nd {
 
@@ -11,7 +11,11 @@ int launch_norm_bf16(const NormArgs& a, cudaStream_t st);
 int launch_norm_f32(const NormArgs& a, cudaStream_t st);
 
 static std::atomic<int> g_tile_rows_override{0};
+static std::atomic<int> g_norm_variant{0};
+static std::atomic<int> g_norm_stages{0};
+int norm_stages_override() { return g_norm_stages.load(std::memory_order_relaxed); }
 int tile_rows_override() { return g_tile_rows_override.load(std::memory_order_relaxed); }
+int norm_variant() { return g_norm_variant.load(std::memory_order_relaxed); }
 
 TilePlan plan_tiles(long long rows, long long row_start, long long seq_len, int tile_rows) {
   TilePlan p{};
@@ -25,23 +29,76 @@ TilePlan plan_tiles(long long rows, long long row_start, long long seq_len, int 
   return p;
 }
 
-// Workspace: [counters: n_samples x u32, padded to 256 B][partials: items x 2 x H fp32], sized for
-// the finest tiling the launcher may choose (8-row tiles, or the override if smaller).
-static size_t counter_bytes(const TilePlan& p) {
-  return (static_cast<size_t>(p.n_samples) * sizeof(unsigned int) + 255) / 256 * 256;
-}
-
-static TilePlan finest_plan(long long rows, long long row_start, long long seq_len) {
+// Workspace of the dparam reduction: fp32 partial column sums, one slot of [2][H] per (chunk, sample)
+// segment of the bulk-copy kernels or per (sample, tile) item of the generic kernels, sized for the
+// larger of the two upper bounds so that the caller need not know which kernel will run.
+static size_t partial_slots(long long rows, long long row_start, long long seq_len) {
   int tr = 8;
   const int forced = tile_rows_override();
   if (forced > 0 && forced < tr) tr = forced;
-  return plan_tiles(rows, row_start, seq_len, tr);
+  const TilePlan p = plan_tiles(rows, row_start, seq_len, tr);
+  const long long chunk_slots = static_cast<long long>(sm_count()) * kMaxChunksPerSm + p.n_samples;
+  return static_cast<size_t>(p.n_items > chunk_slots ? p.n_items : chunk_slots);
 }
 
 static int check_shape(int64_t rows, int64_t row_start, int64_t seq_len, int64_t hidden) {
   if (rows < 0 || row_start < 0 || seq_len <= 0 || hidden <= 0) return ND_ERR_BAD_ARG;
   if (seq_len > INT32_MAX || hidden > INT32_MAX) return ND_ERR_UNSUPPORTED;
   return ND_OK;
+}
+
+// Stage 2 of the dparam reduction (any element type: the partials are fp32). Sample `b_first + blockIdx.y`
+// owns the consecutive workspace slots [first, first + count); they are summed in index order.
+//   chunk scheme (n_chunks > 0): slot = chunk + sample index, chunks = those that overlap the sample's rows;
+//   item scheme  (n_chunks == 0): slot = sample index * tiles_per_sample + tile.
+__global__ void __launch_bounds__(128) norm_dparam_stage2_kernel(const NormArgs a) {
+  const long long bi = blockIdx.y;
+  const long long b = a.b_first + bi;
+  const int H = a.hidden;
+  long long first, count;
+  if (a.n_chunks > 0) {
+    long long s0 = b * a.seq_len - a.row_start, s1 = s0 + a.seq_len;  // the sample's rows, local, clipped below
+    if (s0 < 0) s0 = 0;
+    if (s1 > a.rows) s1 = a.rows;
+    if (s0 >= s1) return;
+    // chunks containing rows s0 and s1 - 1 (start(c) = rows * c / n_chunks is monotone)
+    long long c_lo = s0 * a.n_chunks / a.rows;
+    while (c_lo + 1 < a.n_chunks && chunk_start(a.rows, a.n_chunks, c_lo + 1) <= s0) ++c_lo;
+    while (c_lo > 0 && chunk_start(a.rows, a.n_chunks, c_lo) > s0) --c_lo;
+    long long c_hi = (s1 - 1) * a.n_chunks / a.rows;
+    while (c_hi + 1 < a.n_chunks && chunk_start(a.rows, a.n_chunks, c_hi + 1) <= s1 - 1) ++c_hi;
+    while (c_hi > 0 && chunk_start(a.rows, a.n_chunks, c_hi) > s1 - 1) --c_hi;
+    first = c_lo + bi;
+    count = c_hi - c_lo + 1;
+  } else {
+    first = bi * a.tiles_per_sample;
+    count = a.tiles_per_sample;
+  }
+  const int colx = (blockIdx.x * blockDim.x + threadIdx.x);  // one column of [dscale | dshift] per thread
+  if (colx >= 2 * H) return;
+  const float* src = a.ws_part + first * 2 * H + colx;
+  float acc = 0.f;
+  long long t = 0;
+  for (; t + 4 <= count; t += 4) {  // four independent loads in flight, summed in index order
+    const float v0 = __ldg(src + (t + 0) * 2 * H), v1 = __ldg(src + (t + 1) * 2 * H);
+    const float v2 = __ldg(src + (t + 2) * 2 * H), v3 = __ldg(src + (t + 3) * 2 * H);
+    acc += v0;
+    acc += v1;
+    acc += v2;
+    acc += v3;
+  }
+  for (; t < count; ++t) acc += __ldg(src + t * 2 * H);
+  float* dst = colx < H ? a.dscale + b * H + colx : a.dshift + b * H + (colx - H);
+  *dst = acc;
+}
+
+
+int launch_dparam_stage2(const NormArgs& a, cudaStream_t st) {
+  if (a.n_samples <= 0) return ND_OK;
+  if (a.n_samples > 65535) return ND_ERR_UNSUPPORTED;  // grid.y limit
+  const dim3 grid(static_cast<unsigned>((2 * a.hidden + 127) / 128), static_cast<unsigned>(a.n_samples));
+  norm_dparam_stage2_kernel<<<grid, 128, 0, st>>>(a);
+  return check_launch();
 }
 
 static int dispatch(int dtype, const NormArgs& a, void* stream) {
@@ -91,12 +148,8 @@ static int norm_bwd(bool rms, int mode, int dtype, const void* dy, const void* x
   a.mode = mode; a.rms = rms;
   if (want_dp) {
     const size_t need = nd_norm_dparam_ws_bytes(rows, row_start, seq_len, hidden);
-    if (need > 0) {
-      if (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u)) return ND_ERR_WORKSPACE;
-      const TilePlan p = finest_plan(rows, row_start, seq_len);
-      a.ws_cnt = static_cast<unsigned int*>(ws);
-      a.ws_part = reinterpret_cast<float*>(static_cast<char*>(ws) + counter_bytes(p));
-    }
+    if (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u)) return ND_ERR_WORKSPACE;
+    a.ws_part = static_cast<float*>(ws);
   }
   return dispatch(dtype, a, stream);
 }
@@ -111,31 +164,15 @@ extern "C" {
 // norm kernels (0 restores the built-in choice). Process-wide.
 void nd_tune_norm_tile_rows(int tile_rows) { g_tile_rows_override.store(tile_rows < 0 ? 0 : tile_rows); }
 
-size_t nd_norm_dparam_ws_counter_bytes(int64_t rows, int64_t row_start, int64_t seq_len,
-                                       int64_t hidden) {
-  if (check_shape(rows, row_start, seq_len, hidden) != ND_OK || rows == 0) return 0;
-  return counter_bytes(finest_plan(rows, row_start, seq_len));
-}
+// Tuning hook: which instantiation of the hot norm kernels to launch (rows in flight per thread,
+// prefetch on/off, register cap); 0 = default. Process-wide.
+void nd_tune_norm_variant(int variant) { g_norm_variant.store(variant); }
+// Tuning hook: shared-memory pipeline depth of the bulk-copy norm kernels (0 = as many as fit).
+void nd_tune_norm_stages(int stages) { g_norm_stages.store(stages < 0 ? 0 : stages); }
 
 size_t nd_norm_dparam_ws_bytes(int64_t rows, int64_t row_start, int64_t seq_len, int64_t hidden) {
   if (check_shape(rows, row_start, seq_len, hidden) != ND_OK || rows == 0) return 0;
-  const TilePlan p = finest_plan(rows, row_start, seq_len);
-  if (p.tiles_per_sample <= 1) return 0;
-  return counter_bytes(p) + static_cast<size_t>(p.n_items) * 2 * static_cast<size_t>(hidden) * sizeof(float);
-}
-
-int nd_norm_dparam_ws_init(void* ws, size_t ws_bytes, int64_t rows, int64_t row_start,
-                           int64_t seq_len, int64_t hidden, void* stream) {
-  const size_t need = nd_norm_dparam_ws_bytes(rows, row_start, seq_len, hidden);
-  if (need == 0) return ND_OK;
-  if (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u)) return ND_ERR_WORKSPACE;
-  const size_t cb = nd_norm_dparam_ws_counter_bytes(rows, row_start, seq_len, hidden);
-  cudaError_t e = cudaMemsetAsync(ws, 0, cb, static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) {
-    set_last_cuda_error(e);
-    return ND_ERR_LAUNCH;
-  }
-  return ND_OK;
+  return partial_slots(rows, row_start, seq_len) * 2 * static_cast<size_t>(hidden) * sizeof(float);
 }
 
 int nd_adaln_fwd(int dtype, const void* x, const void* scale, const void* shift, void* y,

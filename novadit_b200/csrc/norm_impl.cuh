@@ -13,10 +13,9 @@
 // Work items. The shard's rows are cut per sample into tiles of `tile_rows`
 // rows; item = (sample, tile). All rows of an item share one sample, so the
 // modulation vector is fetched once per item and kept in registers. The
-// backward pass writes one fp32 partial [2, H] per item and the CTA that
-// finishes a sample's last item sums the partials over tiles in index order
-// (stage 2): deterministic, no floating-point atomics. The only atomic is the
-// integer arrival counter per sample.
+// backward pass writes one fp32 partial [2, H] per item (stage 1) and a second
+// small kernel sums each sample's partials in index order (stage 2):
+// deterministic, no atomics at all.
 #pragma once
 
 #include "common.cuh"
@@ -36,8 +35,7 @@ struct NormArgs {
   void* dx;
   float* dscale;
   float* dshift;
-  float* ws_part;         // [n_items][2][hidden] fp32 partials (when tiles_per_sample > 1)
-  unsigned int* ws_cnt;   // [n_samples] arrival counters, zero on entry and on exit
+  float* ws_part;  // [slots][2][hidden] fp32 partial column sums (stage 1 of the dparam reduction)
   long long rows, row_start;
   int seq_len, hidden;
   float eps;
@@ -45,7 +43,15 @@ struct NormArgs {
   long long b_first, n_samples, n_items;
   int mode;
   bool rms;
+  int n_chunks;  // bulk-copy kernels: the shard's rows are split evenly into this many chunks, one per CTA
+  int stages;    // shared-memory pipeline depth of the bulk-copy kernels
+  int* err;    // device error word (set when a bounded wait expires)
 };
+
+// first row (local to the shard) of chunk c
+__device__ __host__ __forceinline__ long long chunk_start(long long rows, int n_chunks, long long c) {
+  return rows * c / n_chunks;
+}
 
 // rows [l0, l1) (local to the shard) and sample b of a work item
 __device__ __forceinline__ void item_rows(const NormArgs& a, long long item, long long& b,
@@ -201,7 +207,6 @@ template <typename T, int VEC, int CPT, int RPI, int MAXR, bool RMS, bool DX, bo
 __global__ void __maxnreg__(MAXR) norm_bwd_kernel(const NormArgs a) {
   constexpr int Q = RMS ? 1 : 2;  // row sums needed for dx: [sum dxhat,] sum dxhat*xhat
   __shared__ __align__(16) float red[2][Q * RPI * 32];
-  __shared__ int s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
   for (int i = tid; i < 2 * Q * RPI * 32; i += blockDim.x) (&red[0][0])[i] = 0.f;
   __syncthreads();
@@ -335,96 +340,32 @@ __global__ void __maxnreg__(MAXR) norm_bwd_kernel(const NormArgs a) {
     }
 
     if constexpr (DP) {
+      // stage 1 of the dparam reduction: this item's fp32 column sums go to its own slot of the
+      // workspace (zeros if the item lies outside the shard); a second kernel sums each sample's
+      // slots in index order.
       constexpr int FV = (VEC % 4 == 0) ? 4 : 1;  // fp32 partials move as float4 when columns allow
       using FVec = Vec<float, FV>;
-      const int T_ = a.tiles_per_sample;
-      if (T_ == 1) {
-        if (l0 < l1) {
+      float* part = a.ws_part + item * 2 * H;
 #pragma unroll
-          for (int c = 0; c < CPT; ++c) {
-            if (active[c]) {
+      for (int c = 0; c < CPT; ++c) {
+        if (active[c]) {
 #pragma unroll
-              for (int k = 0; k < VEC; k += FV) {
-                FVec vs, vh;
+          for (int k = 0; k < VEC; k += FV) {
+            FVec vs, vh;
 #pragma unroll
-                for (int e = 0; e < FV; ++e) {
-                  vs.v[e] = acc_s[c][k + e];
-                  vh.v[e] = acc_h[c][k + e];
-                }
-                vs.store(a.dscale + b * H + col[c] + k);
-                vh.store(a.dshift + b * H + col[c] + k);
-              }
+            for (int e = 0; e < FV; ++e) {
+              vs.v[e] = acc_s[c][k + e];
+              vh.v[e] = acc_h[c][k + e];
             }
+            vs.store(part + col[c] + k);
+            vh.store(part + H + col[c] + k);
           }
-        }
-      } else {
-        float* part = a.ws_part + item * 2 * H;
-#pragma unroll
-        for (int c = 0; c < CPT; ++c) {
-          if (active[c]) {
-#pragma unroll
-            for (int k = 0; k < VEC; k += FV) {
-              FVec vs, vh;
-#pragma unroll
-              for (int e = 0; e < FV; ++e) {
-                vs.v[e] = acc_s[c][k + e];
-                vh.v[e] = acc_h[c][k + e];
-              }
-              vs.store(part + col[c] + k);
-              vh.store(part + H + col[c] + k);
-            }
-          }
-        }
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-          const unsigned int prev = atomicAdd(a.ws_cnt + bi, 1u);
-          s_last = (prev == static_cast<unsigned int>(T_ - 1)) ? 1 : 0;
-        }
-        __syncthreads();
-        if (s_last) {
-          __threadfence();
-          // stage 2: sum this sample's tile partials in tile order
-          const float* base = a.ws_part + bi * T_ * 2 * H;
-#pragma unroll
-          for (int c = 0; c < CPT; ++c) {
-            if (active[c]) {
-#pragma unroll
-              for (int k = 0; k < VEC; k += FV) {
-                float ts[FV], th[FV];
-#pragma unroll
-                for (int e = 0; e < FV; ++e) ts[e] = th[e] = 0.f;
-                for (int t = 0; t < T_; ++t) {
-                  const float* ps = base + static_cast<long long>(t) * 2 * H + col[c] + k;
-                  if constexpr (FV == 4) {
-                    const float4 u = __ldcg(reinterpret_cast<const float4*>(ps));
-                    const float4 w = __ldcg(reinterpret_cast<const float4*>(ps + H));
-                    ts[0] += u.x; ts[1] += u.y; ts[2] += u.z; ts[3] += u.w;
-                    th[0] += w.x; th[1] += w.y; th[2] += w.z; th[3] += w.w;
-                  } else {
-                    ts[0] += __ldcg(ps);
-                    th[0] += __ldcg(ps + H);
-                  }
-                }
-                FVec vs, vh;
-#pragma unroll
-                for (int e = 0; e < FV; ++e) {
-                  vs.v[e] = ts[e];
-                  vh.v[e] = th[e];
-                }
-                vs.store(a.dscale + b * H + col[c] + k);
-                vh.store(a.dshift + b * H + col[c] + k);
-              }
-            }
-          }
-          if (tid == 0) a.ws_cnt[bi] = 0u;  // leave the counter ready for the next launch
         }
       }
     }
   }
 }
 
-// ------------------------------------------------------------------ launch
 // RPIF / RPIB: rows in flight per thread in the forward / backward kernels; MAXRF / MAXRB: their
 // register caps (threads x registers decides how many CTAs share an SM).
 template <typename T, int VEC, int CPT, int RPIF, int MAXRF, int RPIB, int MAXRB>
@@ -453,71 +394,8 @@ struct TilePlan {
 };
 TilePlan plan_tiles(long long rows, long long row_start, long long seq_len, int tile_rows);
 int tile_rows_override();  // > 0 when a tuning override is set
-
-template <typename T, int VEC>
-int launch_norm_vec(NormArgs a, cudaStream_t st) {
-  const int nvec = a.hidden / VEC;
-  const void* fn = nullptr;
-  int nt = 0;
-  if (nvec <= 256) {
-    fn = pick_kernel<T, VEC, 1, 8, 96, 4, 128>(a.mode, a.rms);
-    nt = (nvec + 31) / 32 * 32;
-  } else if (nvec <= 512) {
-    fn = pick_kernel<T, VEC, 1, 4, 64, 4, 128>(a.mode, a.rms);
-    nt = (nvec + 31) / 32 * 32;
-  } else if (nvec <= 1024) {
-    fn = pick_kernel<T, VEC, 1, 4, 64, 2, 64>(a.mode, a.rms);
-    nt = (nvec + 31) / 32 * 32;
-  } else if (nvec <= 4096) {
-    fn = pick_kernel<T, VEC, 4, 1, 64, 1, 64>(a.mode, a.rms);
-    nt = ((nvec + 3) / 4 + 31) / 32 * 32;
-  } else {
-    return ND_ERR_UNSUPPORTED;
-  }
-
-  // Choose the tile height so that all items fit in one wave of resident CTAs
-  // when the problem is small enough; otherwise use tall tiles and let the
-  // persistent loop spread many items per CTA.
-  int occ = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, nt, 0) != cudaSuccess || occ < 1) {
-    (void)cudaGetLastError();
-    occ = 1;
-  }
-  const long long slots = static_cast<long long>(occ) * sm_count();
-  TilePlan plan{};
-  const int forced = tile_rows_override();
-  if (forced > 0) {
-    plan = plan_tiles(a.rows, a.row_start, a.seq_len, forced);
-  } else {
-    for (int k = 1; k <= 8; ++k) {
-      plan = plan_tiles(a.rows, a.row_start, a.seq_len, 8 * k);
-      if (plan.n_items <= slots) break;
-    }
-  }
-  a.b_first = plan.b_first;
-  a.n_samples = plan.n_samples;
-  a.tile_rows = plan.tile_rows;
-  a.tiles_per_sample = plan.tiles_per_sample;
-  a.n_items = plan.n_items;
-  if (a.n_items == 0) return ND_OK;
-  const long long grid = a.n_items < slots ? a.n_items : slots;
-  void* params[] = {&a};
-  cudaError_t e = cudaLaunchKernel(fn, dim3(static_cast<unsigned>(grid)), dim3(nt), params, 0, st);
-  if (e != cudaSuccess) {
-    set_last_cuda_error(e);
-    (void)cudaGetLastError();
-    return ND_ERR_LAUNCH;
-  }
-  return ND_OK;
-}
-
-template <typename T>
-int launch_norm(const NormArgs& a, cudaStream_t st) {
-  constexpr int VMAX = 16 / sizeof(T);
-  bool vec_ok = (a.hidden % VMAX) == 0;
-  const void* ptrs[] = {a.x, a.scale, a.shift, a.y, a.dy, a.dx, a.dscale, a.dshift, a.ws_part};
-  for (const void* p : ptrs) vec_ok = vec_ok && aligned16(p);
-  return vec_ok ? launch_norm_vec<T, VMAX>(a, st) : launch_norm_vec<T, 1>(a, st);
-}
+int norm_variant();        // tuning: 0 = bulk-copy kernels where they apply, 1 = generic kernels everywhere
+int launch_dparam_stage2(const NormArgs& a, cudaStream_t st);  // fixed-order sum of the stage-1 partials
+constexpr int kMaxChunksPerSm = 8;  // upper bound on resident CTAs per SM used to size the workspace
 
 }  // namespace nd

@@ -1,0 +1,421 @@
+// AdaLN / AdaRMSNorm kernels with a bulk-copy (TMA) pipeline into shared memory (sm_100a).
+//
+// Work split. The shard's rows are cut into `n_chunks` contiguous, equally sized chunks, one
+// per CTA and at most one CTA per resident slot, so a launch is a single balanced wave whatever
+// the batch and sequence sizes are. Inside its chunk a CTA walks groups of up to RPI rows that
+// never cross a sample boundary (the modulation vector and the dscale/dshift column sums are
+// per sample).
+//
+// Data path. The rows of a group are contiguous in global memory, so ONE cp.async.bulk per
+// input tensor lands a whole group in a shared-memory stage. Thread 0 keeps `stages` groups in
+// flight ahead of the consumers: the bytes in flight per SM are set by shared memory (up to
+// ~220 KB), not by registers. All threads wait on the stage's mbarrier, turn their 16-byte
+// column vector of each row into packed fp32 once, and compute; a stage is refilled right
+// after the CTA-wide barrier that follows its last read, so no "empty" barriers exist. Every
+// mbarrier wait is bounded (1 s): on expiry the device error word is set and the whole CTA
+// leaves together.
+//
+// dparam. Each (chunk, sample) segment writes its fp32 column sums to workspace slot
+// chunk + (sample - first sample of the shard); slots of one sample are consecutive, and a second
+// small kernel sums them in index order. No atomics, no fences, deterministic.
+#pragma once
+
+#include "norm_rowmath.cuh"
+#include "ptx.cuh"
+
+namespace nd {
+
+constexpr int kMaxStages = 16;
+constexpr int kBarrierBytes = 128;  // kMaxStages mbarriers at the head of dynamic shared memory
+
+// Walks the row groups of one chunk: groups of up to `rpi` rows that stay inside one sample.
+struct GroupCursor {
+  long long r, r_end;   // next row, end of the chunk (local to the shard)
+  long long b, s_end;   // sample of row r, end of that sample clipped to the chunk (local)
+  __device__ __forceinline__ bool init(const NormArgs& a) {
+    r = chunk_start(a.rows, a.n_chunks, blockIdx.x);
+    r_end = chunk_start(a.rows, a.n_chunks, blockIdx.x + 1);
+    if (r >= r_end) return false;
+    enter_sample(a);
+    return true;
+  }
+  __device__ __forceinline__ void enter_sample(const NormArgs& a) {
+    b = (a.row_start + r) / a.seq_len;
+    const long long e = (b + 1) * a.seq_len - a.row_start;
+    s_end = e < r_end ? e : r_end;
+  }
+  __device__ __forceinline__ int group_rows(int rpi) const {
+    const long long left = s_end - r;
+    return left < rpi ? static_cast<int>(left) : rpi;
+  }
+  // advance past the current group; false at the end of the chunk
+  __device__ __forceinline__ bool next(const NormArgs& a, int rpi) {
+    r += group_rows(rpi);
+    if (r >= r_end) return false;
+    if (r == s_end) enter_sample(a);
+    return true;
+  }
+};
+
+// Issue the bulk copies of the group under `pc` into stage `s` (called by one thread).
+template <typename T, int RPI, bool TWO>
+__device__ __forceinline__ void issue_group(const NormArgs& a, const GroupCursor& pc, int s, uint64_t* full,
+                                            unsigned char* buf, uint32_t row_bytes) {
+  const uint32_t bytes = static_cast<uint32_t>(pc.group_rows(RPI)) * row_bytes;
+  const uint32_t stage_total = (TWO ? 2u : 1u) * RPI * row_bytes;
+  unsigned char* dst = buf + static_cast<size_t>(s) * stage_total;
+  const long long off = pc.r * a.hidden;
+  mbar_expect_tx(&full[s], TWO ? 2 * bytes : bytes);
+  bulk_load_1d(dst, static_cast<const T*>(a.x) + off, bytes, &full[s]);
+  if constexpr (TWO) bulk_load_1d(dst + RPI * row_bytes, static_cast<const T*>(a.dy) + off, bytes, &full[s]);
+}
+
+// Common prologue: barriers, producer cursor, first `stages` groups in flight.
+template <typename T, int RPI, bool TWO>
+__device__ __forceinline__ void pipeline_start(const NormArgs& a, uint64_t* full, unsigned char* buf,
+                                               uint32_t row_bytes, GroupCursor& pc, bool& pc_valid) {
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < a.stages; ++s) mbar_init(&full[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pc_valid = false;
+  if (threadIdx.x == 0) {
+    pc_valid = pc.init(a);
+    for (int s = 0; s < a.stages && pc_valid; ++s) {
+      issue_group<T, RPI, TWO>(a, pc, s, full, buf, row_bytes);
+      pc_valid = pc.next(a, RPI);
+    }
+  }
+}
+
+// A CTA whose wait expired lets copies that may still be in flight land before it exits.
+__device__ __forceinline__ void drain_after_abort() {
+  const unsigned long long t0 = global_ns();
+  while (global_ns() - t0 < 200000ull) __nanosleep(1000);
+}
+
+template <typename T, int VEC, int RPI, int MAXR, bool RMS>
+__global__ void __maxnreg__(MAXR) norm_fwd_tma(const NormArgs a) {
+  constexpr int NP = VEC / 2;
+  extern __shared__ __align__(128) unsigned char dsm[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(dsm);
+  unsigned char* buf = dsm + kBarrierBytes;
+  __shared__ __align__(16) float red[2][RPI * 32];
+  __shared__ __align__(16) float zero16[4];  // what idle lanes of the last warp read instead of a column
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
+  if (tid < 4) zero16[tid] = 0.f;
+
+  const int H = a.hidden;
+  const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
+  const uint32_t stage_total = RPI * row_bytes;
+  const bool active = tid < H / VEC;
+  const int col = active ? tid * VEC : 0;
+  const uint32_t src_stride = active ? row_bytes : 0u;
+  const float inv_h = 1.f / static_cast<float>(H);
+  const float eps = a.eps;
+  const long long row_elems = H;
+  int phase = 0;
+
+  GroupCursor pc;
+  bool pc_valid;
+  pipeline_start<T, RPI, false>(a, full, buf, row_bytes, pc, pc_valid);
+
+  int stage = 0;
+  uint32_t parity = 0;
+  GroupCursor cc;
+  bool more = cc.init(a);
+  while (more) {
+    // per-segment setup: modulation vector of the sample, in registers
+    const long long b = cc.b;
+    float2 sc[NP], sh[NP];
+    {
+      Vec<T, VEC> vs, vh;
+      vs.load(static_cast<const T*>(a.scale) + b * H + col);
+      vh.load(static_cast<const T*>(a.shift) + b * H + col);
+      unpack2<T, VEC>(vs, sc);
+      unpack2<T, VEC>(vh, sh);
+#pragma unroll
+      for (int i = 0; i < NP; ++i) sc[i] = __fadd2_rn(sc[i], make_float2(1.f, 1.f));
+    }
+    do {
+      const long long r = cc.r;
+      const int nrows = cc.group_rows(RPI);
+      const bool arrived = mbar_wait_1s(&full[stage], parity, a.err, 1);
+      if (!__syncthreads_and(arrived)) {
+        drain_after_abort();
+        return;
+      }
+      // this thread's 16-byte column of each row (rows past the group's end hold stale data: they are
+      // reduced like the others, independently per row, and never stored)
+      const unsigned char* src =
+          active ? buf + static_cast<size_t>(stage) * stage_total + col * sizeof(T) : reinterpret_cast<const unsigned char*>(zero16);
+      float2 X[RPI][NP];
+#pragma unroll
+      for (int j = 0; j < RPI; ++j) {
+        Vec<T, VEC> pk;
+        *reinterpret_cast<uint4*>(pk.v) = *reinterpret_cast<const uint4*>(src + j * src_stride);
+        unpack2<T, VEC>(pk, X[j]);
+      }
+
+      float mean_mine[1] = {0.f};
+      bool refilled = false;
+      if constexpr (!RMS) {
+        float s[1][RPI];
+#pragma unroll
+        for (int j = 0; j < RPI; ++j) {
+          float2 acc = X[j][0];
+#pragma unroll
+          for (int i = 1; i < NP; ++i) acc = __fadd2_rn(acc, X[j][i]);
+          s[0][j] = acc.x + acc.y;
+        }
+        cta_sum_rows_post<1, RPI>(s, mean_mine, red[phase], lane, warp, warps,
+                                  [&](int, float t) { return -t * inv_h; });  // broadcast -mean
+        phase ^= 1;
+        if (tid == 0 && pc_valid) {  // every thread has read the stage: refill it
+          fence_proxy_async_smem();
+          issue_group<T, RPI, false>(a, pc, stage, full, buf, row_bytes);
+          pc_valid = pc.next(a, RPI);
+        }
+        refilled = true;
+#pragma unroll
+        for (int j = 0; j < RPI; ++j) {
+          const float2 nm = make_float2(s[0][j], s[0][j]);
+#pragma unroll
+          for (int i = 0; i < NP; ++i) X[j][i] = __fadd2_rn(X[j][i], nm);  // deviations, in place
+        }
+      }
+
+      float q[1][RPI], rstd_mine[1];
+#pragma unroll
+      for (int j = 0; j < RPI; ++j) {
+        float2 acc = __fmul2_rn(X[j][0], X[j][0]);
+#pragma unroll
+        for (int i = 1; i < NP; ++i) acc = __ffma2_rn(X[j][i], X[j][i], acc);
+        q[0][j] = active ? acc.x + acc.y : 0.f;  // an idle lane's deviations are -mean, not 0
+      }
+      cta_sum_rows_post<1, RPI>(q, rstd_mine, red[phase], lane, warp, warps,
+                                [&](int, float t) { return rsqrt_newton(fmaf(t, inv_h, eps)); });  // broadcast 1/std
+      phase ^= 1;
+      if (!refilled && tid == 0 && pc_valid) {
+        fence_proxy_async_smem();
+        issue_group<T, RPI, false>(a, pc, stage, full, buf, row_bytes);
+        pc_valid = pc.next(a, RPI);
+      }
+
+      if (tid < RPI && tid < nrows && a.invstd != nullptr) {  // lane j of warp 0 owns row j's statistics
+        if constexpr (!RMS) a.mean[r + tid] = -mean_mine[0];
+        a.invstd[r + tid] = rstd_mine[0];
+      }
+      if (active) {
+        T* yp = static_cast<T*>(a.y) + r * row_elems + col;
+#pragma unroll
+        for (int j = 0; j < RPI; ++j) {
+          if (j < nrows) {
+            const float2 r2 = make_float2(q[0][j], q[0][j]);
+            float2 out[NP];
+#pragma unroll
+            for (int i = 0; i < NP; ++i) out[i] = __ffma2_rn(__fmul2_rn(X[j][i], r2), sc[i], sh[i]);
+            Vec<T, VEC> o;
+            pack2<T, VEC>(out, o);
+            o.store(yp);
+          }
+          yp += row_elems;
+        }
+      }
+      if (++stage == a.stages) {
+        stage = 0;
+        parity ^= 1u;
+      }
+      more = cc.next(a, RPI);
+    } while (more && cc.b == b);
+  }
+}
+
+template <typename T, int VEC, int RPI, int MAXR, bool RMS, bool DX, bool DP>
+__global__ void __maxnreg__(MAXR) norm_bwd_tma(const NormArgs a) {
+  constexpr int NP = VEC / 2;
+  constexpr int Q = RMS ? 1 : 2;  // row sums needed for dx: [sum dxhat,] sum dxhat*xhat
+  extern __shared__ __align__(128) unsigned char dsm[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(dsm);
+  unsigned char* buf = dsm + kBarrierBytes;
+  __shared__ __align__(16) float red[2][Q * RPI * 32];
+  __shared__ __align__(16) float zero16[4];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
+  if (tid < 4) zero16[tid] = 0.f;
+
+  const int H = a.hidden;
+  const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
+  const uint32_t stage_total = 2 * RPI * row_bytes;  // x rows then dy rows
+  const bool active = tid < H / VEC;
+  const int col = active ? tid * VEC : 0;
+  const uint32_t src_stride = active ? row_bytes : 0u;
+  const uint32_t dy_off = active ? RPI * row_bytes : 0u;
+  const float inv_h = 1.f / static_cast<float>(H);
+  const long long row_elems = H;
+  int phase = 0;
+
+  GroupCursor pc;
+  bool pc_valid;
+  pipeline_start<T, RPI, true>(a, full, buf, row_bytes, pc, pc_valid);
+  int stage = 0;
+  uint32_t parity = 0;
+
+  GroupCursor cc;
+  bool more = cc.init(a);
+  while (more) {
+    // one segment = the rows of one sample inside this chunk
+    const long long b = cc.b;
+    float2 sc1[NP], acc_s[NP], acc_h[NP];
+#pragma unroll
+    for (int i = 0; i < NP; ++i) acc_s[i] = acc_h[i] = make_float2(0.f, 0.f);
+    if constexpr (DX) {
+      Vec<T, VEC> vs;
+      vs.load(static_cast<const T*>(a.scale) + b * H + col);
+      unpack2<T, VEC>(vs, sc1);
+#pragma unroll
+      for (int i = 0; i < NP; ++i) sc1[i] = __fadd2_rn(sc1[i], make_float2(1.f, 1.f));
+    }
+
+    do {
+      const long long r = cc.r;
+      const int nrows = cc.group_rows(RPI);
+      const bool full_group = nrows == RPI;
+      float rstd[RPI], nmean[RPI];
+#pragma unroll
+      for (int j = 0; j < RPI; ++j) {
+        const long long rr = r + (j < nrows ? j : nrows - 1);  // clamped inside the group
+        rstd[j] = __ldg(a.invstd + rr);
+        if constexpr (!RMS) nmean[j] = -__ldg(a.mean + rr);
+        else nmean[j] = 0.f;
+      }
+      const bool arrived = mbar_wait_1s(&full[stage], parity, a.err, 2);
+      if (!__syncthreads_and(arrived)) {
+        drain_after_abort();
+        return;
+      }
+      const unsigned char* src =
+          active ? buf + static_cast<size_t>(stage) * stage_total + col * sizeof(T) : reinterpret_cast<const unsigned char*>(zero16);
+      float2 X[RPI][NP], G[RPI][NP];
+#pragma unroll
+      for (int j = 0; j < RPI; ++j) {
+        Vec<T, VEC> px, pg;
+        *reinterpret_cast<uint4*>(px.v) = *reinterpret_cast<const uint4*>(src + j * src_stride);
+        *reinterpret_cast<uint4*>(pg.v) = *reinterpret_cast<const uint4*>(src + dy_off + j * src_stride);
+        unpack2<T, VEC>(px, X[j]);
+        unpack2<T, VEC>(pg, G[j]);
+      }
+      if (!full_group) {  // rows past the group's end hold stale data: keep them out of the column sums
+#pragma unroll
+        for (int j = 0; j < RPI; ++j) {
+          if (j >= nrows) {
+#pragma unroll
+            for (int i = 0; i < NP; ++i) {
+              G[j][i] = make_float2(0.f, 0.f);
+              X[j][i] = make_float2(0.f, 0.f);
+            }
+          }
+        }
+      }
+
+      float p[Q][RPI];
+#pragma unroll
+      for (int j = 0; j < RPI; ++j) {
+        const float2 r2 = make_float2(rstd[j], rstd[j]), m2 = make_float2(nmean[j], nmean[j]);
+        float2 p0 = make_float2(0.f, 0.f), p1 = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+          // xhat = (x - mean) * rstd in place (idle lanes read zeros: dy = 0 makes every product 0)
+          if constexpr (!RMS) X[j][i] = __fadd2_rn(X[j][i], m2);
+          X[j][i] = __fmul2_rn(X[j][i], r2);
+          if constexpr (DP) {
+            acc_h[i] = __fadd2_rn(acc_h[i], G[j][i]);
+            acc_s[i] = __ffma2_rn(G[j][i], X[j][i], acc_s[i]);
+          }
+          if constexpr (DX) {
+            G[j][i] = __fmul2_rn(G[j][i], sc1[i]);  // dxhat in place
+            if constexpr (!RMS) p0 = __fadd2_rn(p0, G[j][i]);
+            p1 = __ffma2_rn(G[j][i], X[j][i], p1);
+          }
+        }
+        if constexpr (DX) {
+          if constexpr (!RMS) p[0][j] = p0.x + p0.y;
+          p[Q - 1][j] = p1.x + p1.y;
+        }
+      }
+      if constexpr (DX) {
+        float mine[Q];
+        cta_sum_rows_post<Q, RPI>(p, mine, red[phase], lane, warp, warps,
+                                  [&](int, float t) { return -t * inv_h; });  // broadcast -mean_h(.)
+        phase ^= 1;
+      } else {
+        __syncthreads();  // every thread has read the stage
+      }
+      if (tid == 0 && pc_valid) {
+        fence_proxy_async_smem();
+        issue_group<T, RPI, true>(a, pc, stage, full, buf, row_bytes);
+        pc_valid = pc.next(a, RPI);
+      }
+      if (++stage == a.stages) {
+        stage = 0;
+        parity ^= 1u;
+      }
+      if constexpr (DX) {
+        if (active) {
+          T* dp = static_cast<T*>(a.dx) + r * row_elems + col;
+#pragma unroll
+          for (int j = 0; j < RPI; ++j) {
+            if (j < nrows) {
+              const float2 c2v = make_float2(p[Q - 1][j], p[Q - 1][j]), r2 = make_float2(rstd[j], rstd[j]);
+              float2 out[NP];
+#pragma unroll
+              for (int i = 0; i < NP; ++i) {
+                float2 t = G[j][i];
+                if constexpr (!RMS) t = __fadd2_rn(t, make_float2(p[0][j], p[0][j]));
+                t = __ffma2_rn(X[j][i], c2v, t);
+                out[i] = __fmul2_rn(t, r2);
+              }
+              Vec<T, VEC> o;
+              pack2<T, VEC>(out, o);
+              o.store(dp);
+            }
+            dp += row_elems;
+          }
+        }
+      }
+      more = cc.next(a, RPI);
+    } while (more && cc.b == b);
+
+    if constexpr (DP) {
+      // stage 1 of the dparam reduction: this segment's column sums go to their own workspace slot
+      if (active) {
+        constexpr int NF4 = VEC / 4;  // float4 chunks per thread (VEC is 4 or 8)
+        float* part = a.ws_part + (static_cast<long long>(blockIdx.x) + (b - a.b_first)) * 2 * H + col;
+#pragma unroll
+        for (int k = 0; k < NF4; ++k) {
+          reinterpret_cast<float4*>(part)[k] = make_float4(acc_s[2 * k].x, acc_s[2 * k].y, acc_s[2 * k + 1].x, acc_s[2 * k + 1].y);
+          reinterpret_cast<float4*>(part + H)[k] = make_float4(acc_h[2 * k].x, acc_h[2 * k].y, acc_h[2 * k + 1].x, acc_h[2 * k + 1].y);
+        }
+      }
+    }
+  }
+}
+
+template <typename T, int VEC, int RPI, int MAXRF, int MAXRB>
+static const void* pick_tma(int mode, bool rms) {
+  switch (mode) {
+    case kFwd:
+      return rms ? (const void*)norm_fwd_tma<T, VEC, RPI, MAXRF, true> : (const void*)norm_fwd_tma<T, VEC, RPI, MAXRF, false>;
+    case kBwdDx:
+      return rms ? (const void*)norm_bwd_tma<T, VEC, RPI, MAXRB, true, true, false>
+                 : (const void*)norm_bwd_tma<T, VEC, RPI, MAXRB, false, true, false>;
+    case kBwdDparam:
+      return rms ? (const void*)norm_bwd_tma<T, VEC, RPI, MAXRB, true, false, true>
+                 : (const void*)norm_bwd_tma<T, VEC, RPI, MAXRB, false, false, true>;
+    default:
+      return rms ? (const void*)norm_bwd_tma<T, VEC, RPI, MAXRB, true, true, true>
+                 : (const void*)norm_bwd_tma<T, VEC, RPI, MAXRB, false, true, true>;
+  }
+}
+
+}  // namespace nd

@@ -1,11 +1,34 @@
 // Process-wide helpers of the C ABI: status strings, last CUDA error, device facts.
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace nd {
+
+__device__ int g_device_error = 0;  // set by a kernel whose bounded wait expired
 
 static thread_local int t_last_cuda_error = 0;
 
 void set_last_cuda_error(cudaError_t e) { t_last_cuda_error = static_cast<int>(e); }
+
+// Device address of the error word of the current device (nullptr if it cannot be resolved).
+int* device_error_ptr() {
+  constexpr int kMaxDevices = 64;
+  static int* cache[kMaxDevices] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  if (cache[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_device_error) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    cache[dev] = static_cast<int*>(p);
+  }
+  return cache[dev];
+}
 
 int sm_count() {
   constexpr int kMaxDevices = 64;
@@ -45,5 +68,18 @@ const char* nd_status_string(int status) {
 int nd_last_cuda_error(void) { return nd::t_last_cuda_error; }
 
 int nd_version(void) { return 100; }
+
+int nd_device_error(int reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, nd::g_device_error, sizeof(int)) != cudaSuccess) {
+    nd::set_last_cuda_error(cudaGetLastError());
+    return ND_ERR_LAUNCH;
+  }
+  if (reset && v != 0) {
+    const int zero = 0;
+    (void)cudaMemcpyToSymbol(nd::g_device_error, &zero, sizeof(int));
+  }
+  return v;
+}
 
 }  // extern "C"

@@ -92,11 +92,7 @@ void check_norm_backward(const at::Tensor& dy, const at::Tensor& x, const at::Te
 at::Tensor dparam_workspace(const at::Tensor& x, size_t* bytes) {
   const int64_t rows = x.size(0) * x.size(1);
   *bytes = nd_norm_dparam_ws_bytes(rows, 0, x.size(1), x.size(2));
-  at::Tensor ws = at::empty({static_cast<int64_t>(*bytes)}, x.options().dtype(at::kByte));
-  if (*bytes > 0)
-    check_status(nd_norm_dparam_ws_init(ws.data_ptr(), *bytes, rows, 0, x.size(1), x.size(2), current_stream(x)),
-                 "workspace init");
-  return ws;
+  return at::empty({static_cast<int64_t>(*bytes)}, x.options().dtype(at::kByte));
 }
 
 // ------------------------------------------------------------------ norm forward

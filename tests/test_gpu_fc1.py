@@ -57,8 +57,9 @@ def test_matches_oracle(act, layout, dtype, mkn, bias):
     m, k, n = mkn
     x, w, b = synth.fc1_inputs(m, k, n, dtype, seed=50 + m % 7)
     y = run(x, w, b if bias else None, act, layout)
-    want = oracle.fc1_fwd(x, w, b if bias else None, act, gated=layout != 0, compute=torch.float64)
-    assert_half_parity(y, want, f"fc1 {act} layout {layout} {dtype} {mkn}")
+    exact = oracle.fc1_fwd(x, w, b if bias else None, act, gated=layout != 0, compute=torch.float64,
+                           out_dtype=torch.float64)
+    assert_half_parity(y, exact.to(dtype), f"fc1 {act} layout {layout} {dtype} {mkn}", exact=exact)
 
 
 @pytest.mark.parametrize("layout", [0, 1])
@@ -66,8 +67,8 @@ def test_config4_bf16(layout):
     """Workload config 4: M=8192, K=1152, N=4608, bias, GELU-tanh, bf16 (gated as in the reference, and plain)."""
     x, w, b = synth.fc1_inputs(8192, 1152, 4608, torch.bfloat16, seed=0)
     y = run(x, w, b, "gelu", layout)
-    want = oracle.fc1_fwd(x, w, b, "gelu", gated=layout != 0)
-    assert_half_parity(y, want, f"config4 layout {layout}")
+    exact = oracle.fc1_fwd(x, w, b, "gelu", gated=layout != 0, compute=torch.float64, out_dtype=torch.float64)
+    assert_half_parity(y, exact.to(torch.bfloat16), f"config4 layout {layout}", exact=exact)
 
 
 @pytest.mark.parametrize("layout", [0, 1])
@@ -108,8 +109,9 @@ def test_large_case_properties():
     assert int(status.item()) == 0
     rows = torch.randint(0, m, (256,), generator=g, device=DEV)
     xs = x[rows].contiguous()
-    want = oracle.fc1_fwd(xs.cpu(), w.cpu(), b.cpu(), "gelu", gated=True)
-    assert_half_parity(y[rows].cpu(), want, "large case sampled rows")
+    exact = oracle.fc1_fwd(xs.cpu(), w.cpu(), b.cpu(), "gelu", gated=True, compute=torch.float64,
+                           out_dtype=torch.float64)
+    assert_half_parity(y[rows].cpu(), exact.to(torch.bfloat16), "large case sampled rows", exact=exact)
     # the same rows computed as their own small problem give the same bits
     assert torch.equal(capi.fc1_fwd(xs, w, b, "gelu", 1), y[rows])
 

@@ -23,9 +23,9 @@ def run_fwd_bwd(kind, x, scale, shift, dy, eps, mode="fused", **kw):
     xd, sd, hd, gd = (t.to(DEV).contiguous() for t in (x, scale, shift, dy))
     sd2, hd2 = sd.reshape(sd.shape[0], -1), hd.reshape(hd.shape[0], -1)
     if kind == "layer":
-        y, mean, invstd = capi.norm_fwd(kind, xd, sd2, hd2, eps, **kw)
+        y, mean, invstd = capi.norm_fwd(kind, xd, sd2, hd2, eps)
     else:
-        y, invstd = capi.norm_fwd(kind, xd, sd2, hd2, eps, **kw)
+        y, invstd = capi.norm_fwd(kind, xd, sd2, hd2, eps)
         mean = None
     dx, dscale, dshift = capi.norm_bwd(kind, gd, xd, sd2, mean, invstd, mode=mode, **kw)
     torch.cuda.synchronize()
@@ -33,21 +33,27 @@ def run_fwd_bwd(kind, x, scale, shift, dy, eps, mode="fused", **kw):
 
 
 def oracle_fwd_bwd(kind, x, scale, shift, dy, eps, compute=torch.float64):
+    """(y, mean, invstd, dx, dscale, dshift, y_exact, dx_exact): fp64 oracle, rounded once, plus the
+    unrounded fp64 values used to recognise rounding near-ties."""
     if kind == "layer":
-        y, mean, invstd = oracle.adaln_fwd(x, scale, shift, eps, compute=compute)
-        dx, ds, dh = oracle.adaln_bwd(dy, x, scale, eps, compute=compute)
+        ye, mean, invstd = oracle.adaln_fwd(x, scale, shift, eps, compute=compute, round_out=False)
+        dxe, ds, dh = oracle.adaln_bwd(dy, x, scale, eps, compute=compute, round_out=False)
     else:
-        y, invstd = oracle.adarms_fwd(x, scale, shift, eps, compute=compute)
+        ye, invstd = oracle.adarms_fwd(x, scale, shift, eps, compute=compute, round_out=False)
         mean = None
-        dx, ds, dh = oracle.adarms_bwd(dy, x, scale, eps, compute=compute)
-    return y, mean, invstd, dx, ds, dh
+        dxe, ds, dh = oracle.adarms_bwd(dy, x, scale, eps, compute=compute, round_out=False)
+    return ye.to(x.dtype), mean, invstd, dxe.to(x.dtype), ds, dh, ye, dxe
 
 
 def compare_all(kind, got, want, what):
     y, mean, invstd, dx, ds, dh = got
-    wy, wmean, winvstd, wdx, wds, wdh = want
-    assert_parity(y, wy, what + " y")
-    assert_parity(dx, wdx, what + " dx")
+    wy, wmean, winvstd, wdx, wds, wdh, ye, dxe = want
+    if wy.dtype == torch.float32:
+        assert_parity(y, wy, what + " y")
+        assert_parity(dx, wdx, what + " dx")
+    else:
+        assert_half_parity(y, wy, what + " y", exact=ye)
+        assert_half_parity(dx, wdx, what + " dx", exact=dxe)
     if kind == "layer":
         assert_f32_parity(mean.reshape(wmean.shape), wmean, what + " mean", tol=1e-4 + 0.0)
     assert_f32_parity(invstd.reshape(winvstd.shape), winvstd, what + " invstd", tol=1e-5)
@@ -117,6 +123,29 @@ def test_inference_equals_training_output_bitwise(kind):
     y_train = capi.norm_fwd(kind, xd, sd, hd, 1e-5)[0]
     y_inf = capi.norm_fwd(kind, xd, sd, hd, 1e-5, stats=False)[0]
     assert torch.equal(y_train, y_inf)
+
+
+@pytest.mark.parametrize("kind", ["layer", "rms"])
+@pytest.mark.parametrize("variant", [0, 1])
+def test_every_kernel_variant_meets_the_bars(kind, variant):
+    """The tuning knob selects among instantiations of the hot kernels; each must be correct."""
+    x, scale, shift, dy = synth.norm_inputs(5, 77, 1152, torch.bfloat16, 8)
+    want = oracle_fwd_bwd(kind, x, scale, shift, dy, 1e-6)
+    L = capi.lib()
+    try:
+        L.nd_tune_norm_variant(variant)
+        for mode in ("fused", "dx", "dparam"):
+            got = run_fwd_bwd(kind, x, scale, shift, dy, 1e-6, mode=mode)
+            if mode == "fused":
+                compare_all(kind, got, want, f"variant {variant}")
+            elif mode == "dx":
+                assert_half_parity(got[3], want[3], f"variant {variant} dx only", exact=want[7])
+            else:
+                assert_f32_parity(got[4], want[4], f"variant {variant} dscale only")
+                assert_f32_parity(got[5], want[5], f"variant {variant} dshift only")
+        assert L.nd_device_error(0) == 0, "a bounded device-side wait expired"
+    finally:
+        L.nd_tune_norm_variant(0)
 
 
 @pytest.mark.parametrize("tile_rows", [1, 8, 24, 64, 1000])
@@ -191,7 +220,7 @@ def test_empty_shard_and_bad_arguments():
     big = torch.zeros(64, 8, dtype=torch.bfloat16, device=DEV)
     stat = torch.zeros(64, dtype=torch.float32, device=DEV)
     out = torch.zeros(1, 8, dtype=torch.float32, device=DEV)
-    assert L.nd_norm_dparam_ws_bytes(64, 0, 64, 8) > 0
+    assert L.nd_norm_dparam_ws_bytes(64, 0, 64, 8) > 0 and L.nd_norm_dparam_ws_bytes(0, 0, 64, 8) == 0
     assert L.nd_adaln_bwd_dparam(capi.ND_BF16, big.data_ptr(), big.data_ptr(), stat.data_ptr(), stat.data_ptr(),
                                  out.data_ptr(), out.data_ptr(), 64, 0, 64, 8, None, 0, st) == -4
     torch.cuda.synchronize()
