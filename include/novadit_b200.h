@@ -60,6 +60,11 @@ void nd_tune_norm_variant(int variant);
 /* Tuning hook: pipeline depth (shared-memory stages) of the bulk-copy norm kernels; 0 = as many as
  * fit the per-CTA budget. No counterpart in the reference. */
 void nd_tune_norm_stages(int stages);
+/* Tuning hook: 0 launches the norm kernels without programmatic stream serialization (default 1:
+ * each kernel may be scheduled while its predecessor in the stream drains). */
+void nd_tune_norm_pdl(int enabled);
+/* Tuning hook: cap on CTAs per SM of the bulk-copy norm kernels (0 = what occupancy allows). */
+void nd_tune_norm_chunks_per_sm(int n);
 
 /* ------------------------------------------------------------------ AdaLN */
 

@@ -32,6 +32,8 @@ SIGNATURES = {
     "nd_tune_norm_tile_rows": (None, [c_int]),
     "nd_tune_norm_variant": (None, [c_int]),
     "nd_tune_norm_stages": (None, [c_int]),
+    "nd_tune_norm_pdl": (None, [c_int]),
+    "nd_tune_norm_chunks_per_sm": (None, [c_int]),
     "nd_adaln_fwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              *_SHAPE4, c_float, c_void_p]),
     "nd_adaln_bwd_dx": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

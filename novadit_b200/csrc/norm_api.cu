@@ -14,6 +14,10 @@ static std::atomic<int> g_tile_rows_override{0};
 static std::atomic<int> g_norm_variant{0};
 static std::atomic<int> g_norm_stages{0};
 int norm_stages_override() { return g_norm_stages.load(std::memory_order_relaxed); }
+static std::atomic<int> g_norm_cps{0};
+int norm_chunks_per_sm() { return g_norm_cps.load(std::memory_order_relaxed); }
+static std::atomic<int> g_norm_pdl{1};
+int norm_pdl_enabled() { return g_norm_pdl.load(std::memory_order_relaxed); }
 int tile_rows_override() { return g_tile_rows_override.load(std::memory_order_relaxed); }
 int norm_variant() { return g_norm_variant.load(std::memory_order_relaxed); }
 
@@ -52,6 +56,8 @@ static int check_shape(int64_t rows, int64_t row_start, int64_t seq_len, int64_t
 //   chunk scheme (n_chunks > 0): slot = chunk + sample index, chunks = those that overlap the sample's rows;
 //   item scheme  (n_chunks == 0): slot = sample index * tiles_per_sample + tile.
 __global__ void __launch_bounds__(128) norm_dparam_stage2_kernel(const NormArgs a) {
+  griddep_launch_dependents();
+  griddep_wait();  // the partials come from the kernel launched just before
   const long long bi = blockIdx.y;
   const long long b = a.b_first + bi;
   const int H = a.hidden;
@@ -61,13 +67,10 @@ __global__ void __launch_bounds__(128) norm_dparam_stage2_kernel(const NormArgs 
     if (s0 < 0) s0 = 0;
     if (s1 > a.rows) s1 = a.rows;
     if (s0 >= s1) return;
-    // chunks containing rows s0 and s1 - 1 (start(c) = rows * c / n_chunks is monotone)
-    long long c_lo = s0 * a.n_chunks / a.rows;
-    while (c_lo + 1 < a.n_chunks && chunk_start(a.rows, a.n_chunks, c_lo + 1) <= s0) ++c_lo;
-    while (c_lo > 0 && chunk_start(a.rows, a.n_chunks, c_lo) > s0) --c_lo;
-    long long c_hi = (s1 - 1) * a.n_chunks / a.rows;
-    while (c_hi + 1 < a.n_chunks && chunk_start(a.rows, a.n_chunks, c_hi + 1) <= s1 - 1) ++c_hi;
-    while (c_hi > 0 && chunk_start(a.rows, a.n_chunks, c_hi) > s1 - 1) --c_hi;
+    // chunk holding row s: the first chunk_rem chunks have chunk_base + 1 rows, the others chunk_base
+    const long long big = static_cast<long long>(a.chunk_rem) * (a.chunk_base + 1);
+    auto chunk_of = [&](long long s) { return s < big ? s / (a.chunk_base + 1) : a.chunk_rem + (s - big) / a.chunk_base; };
+    const long long c_lo = chunk_of(s0), c_hi = chunk_of(s1 - 1);
     first = c_lo + bi;
     count = c_hi - c_lo + 1;
   } else {
@@ -77,28 +80,33 @@ __global__ void __launch_bounds__(128) norm_dparam_stage2_kernel(const NormArgs 
   const int colx = (blockIdx.x * blockDim.x + threadIdx.x);  // one column of [dscale | dshift] per thread
   if (colx >= 2 * H) return;
   const float* src = a.ws_part + first * 2 * H + colx;
+  const long long stride = 2LL * H;
   float acc = 0.f;
   long long t = 0;
-  for (; t + 4 <= count; t += 4) {  // four independent loads in flight, summed in index order
-    const float v0 = __ldg(src + (t + 0) * 2 * H), v1 = __ldg(src + (t + 1) * 2 * H);
-    const float v2 = __ldg(src + (t + 2) * 2 * H), v3 = __ldg(src + (t + 3) * 2 * H);
-    acc += v0;
-    acc += v1;
-    acc += v2;
-    acc += v3;
+  for (; t + 8 <= count; t += 8) {  // eight independent loads in flight, summed in index order
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = __ldcg(src + (t + u) * stride);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc += v[u];
   }
-  for (; t < count; ++t) acc += __ldg(src + t * 2 * H);
+  {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = t + u < count ? __ldcg(src + (t + u) * stride) : 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc += v[u];  // adding +0 keeps the order and the value
+  }
   float* dst = colx < H ? a.dscale + b * H + colx : a.dshift + b * H + (colx - H);
   *dst = acc;
 }
-
 
 int launch_dparam_stage2(const NormArgs& a, cudaStream_t st) {
   if (a.n_samples <= 0) return ND_OK;
   if (a.n_samples > 65535) return ND_ERR_UNSUPPORTED;  // grid.y limit
   const dim3 grid(static_cast<unsigned>((2 * a.hidden + 127) / 128), static_cast<unsigned>(a.n_samples));
-  norm_dparam_stage2_kernel<<<grid, 128, 0, st>>>(a);
-  return check_launch();
+  NormArgs copy = a;
+  return launch_checked(reinterpret_cast<const void*>(norm_dparam_stage2_kernel), 0, 128, copy, 0, st, grid);
 }
 
 static int dispatch(int dtype, const NormArgs& a, void* stream) {
@@ -169,6 +177,10 @@ void nd_tune_norm_tile_rows(int tile_rows) { g_tile_rows_override.store(tile_row
 void nd_tune_norm_variant(int variant) { g_norm_variant.store(variant); }
 // Tuning hook: shared-memory pipeline depth of the bulk-copy norm kernels (0 = as many as fit).
 void nd_tune_norm_stages(int stages) { g_norm_stages.store(stages < 0 ? 0 : stages); }
+// Tuning hook: 0 launches the norm kernels without programmatic stream serialization (default 1).
+void nd_tune_norm_pdl(int enabled) { g_norm_pdl.store(enabled != 0); }
+// Tuning hook: cap on CTAs per SM of the bulk-copy norm kernels (0 = what occupancy allows).
+void nd_tune_norm_chunks_per_sm(int n) { g_norm_cps.store(n < 0 ? 0 : n); }
 
 size_t nd_norm_dparam_ws_bytes(int64_t rows, int64_t row_start, int64_t seq_len, int64_t hidden) {
   if (check_shape(rows, row_start, seq_len, hidden) != ND_OK || rows == 0) return 0;

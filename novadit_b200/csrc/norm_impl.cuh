@@ -19,6 +19,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace nd {
 
@@ -44,13 +45,16 @@ struct NormArgs {
   int mode;
   bool rms;
   int n_chunks;  // bulk-copy kernels: the shard's rows are split evenly into this many chunks, one per CTA
+  long long chunk_base;  // rows / n_chunks
+  int chunk_rem;         // rows % n_chunks
   int stages;    // shared-memory pipeline depth of the bulk-copy kernels
   int* err;    // device error word (set when a bounded wait expires)
 };
 
 // first row (local to the shard) of chunk c
-__device__ __host__ __forceinline__ long long chunk_start(long long rows, int n_chunks, long long c) {
-  return rows * c / n_chunks;
+// (chunks differ in size by at most one row: the first `chunk_rem` chunks hold `chunk_base` + 1 rows)
+__device__ __host__ __forceinline__ long long chunk_start(long long chunk_base, int chunk_rem, long long c) {
+  return c * chunk_base + (c < chunk_rem ? c : chunk_rem);
 }
 
 // rows [l0, l1) (local to the shard) and sample b of a work item
@@ -73,7 +77,9 @@ __global__ void __maxnreg__(MAXR) norm_fwd_kernel(const NormArgs a) {
   __shared__ __align__(16) float red[2][RPI * 32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
   for (int i = tid; i < 2 * RPI * 32; i += blockDim.x) (&red[0][0])[i] = 0.f;
+  griddep_launch_dependents();
   __syncthreads();
+  griddep_wait();
 
   const int H = a.hidden;
   const int nvec = H / VEC;
@@ -209,7 +215,9 @@ __global__ void __maxnreg__(MAXR) norm_bwd_kernel(const NormArgs a) {
   __shared__ __align__(16) float red[2][Q * RPI * 32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
   for (int i = tid; i < 2 * Q * RPI * 32; i += blockDim.x) (&red[0][0])[i] = 0.f;
+  griddep_launch_dependents();
   __syncthreads();
+  griddep_wait();
 
   const int H = a.hidden;
   const int nvec = H / VEC;

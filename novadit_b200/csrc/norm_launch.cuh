@@ -13,9 +13,26 @@ namespace nd {
 
 int norm_stages_override();  // tuning: pipeline depth of the bulk-copy kernels (0 = by budget)
 
-inline int launch_checked(const void* fn, long long grid, int nt, NormArgs& a, int smem, cudaStream_t st) {
+int norm_pdl_enabled();      // tuning: launch with programmatic stream serialization (default on)
+int norm_chunks_per_sm();    // tuning: cap on CTAs per SM for the bulk-copy kernels (0 = occupancy)
+
+// Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor
+// in the stream drains (every norm kernel executes griddepcontrol.wait before its first global read),
+// which hides the launch latency between the forward, backward and stage-2 kernels of a step.
+inline int launch_checked(const void* fn, long long grid, int nt, NormArgs& a, int smem, cudaStream_t st,
+                          dim3 grid3 = dim3(0)) {
   void* params[] = {&a};
-  cudaError_t e = cudaLaunchKernel(fn, dim3(static_cast<unsigned>(grid)), dim3(nt), params, smem, st);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid3.x != 0 ? grid3 : dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(nt);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = norm_pdl_enabled() ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelExC(&cfg, fn, params);
   if (e != cudaSuccess) {
     set_last_cuda_error(e);
     (void)cudaGetLastError();
@@ -24,13 +41,16 @@ inline int launch_checked(const void* fn, long long grid, int nt, NormArgs& a, i
   return ND_OK;
 }
 
-inline long long resident_slots(const void* fn, int nt, int smem) {
+inline long long resident_slots(const void* fn, int nt, int smem, bool fwd = true) {
   int occ = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, nt, smem) != cudaSuccess || occ < 1) {
     (void)cudaGetLastError();
     occ = 1;
   }
   if (occ > kMaxChunksPerSm) occ = kMaxChunksPerSm;  // the workspace is sized for this many CTAs per SM
+  const int knob = norm_chunks_per_sm();  // n < 10: cap for both passes; otherwise tens = forward cap, units = backward cap
+  const int cap = knob < 10 ? knob : (fwd ? knob / 10 : knob % 10);
+  if (cap > 0 && occ > cap) occ = cap;
   return static_cast<long long>(occ) * sm_count();
 }
 
@@ -39,12 +59,16 @@ int launch_norm_tma(NormArgs a, cudaStream_t st) {
   constexpr int RPI = 4;
   const int nvec = a.hidden / VEC;
   const int nt = (nvec + 31) / 32 * 32;
-  const void* fn = pick_tma<T, VEC, RPI, 96, 136>(a.mode, a.rms);
+  // 128 registers per backward thread: three 160-thread CTAs per SM, and 512-thread CTAs still launch
+  const void* fn = pick_tma<T, VEC, RPI, 96, 128>(a.mode, a.rms);
   // as many pipeline stages as fit the per-CTA shared-memory budget (4 forward / 3 backward CTAs per SM)
   const int tensors = a.mode == kFwd ? 1 : 2;
   const int stage_bytes = tensors * RPI * a.hidden * static_cast<int>(sizeof(T));
+  // Two stages measured best at the DiT-XL/2 shape: deeper pipelines hold shared memory that the
+  // next kernel's CTAs (programmatic dependent launch) could otherwise start in. Never more than fits.
   const int budget = a.mode == kFwd ? 54 * 1024 : 72 * 1024;
-  int stages = norm_stages_override() > 0 ? norm_stages_override() : budget / stage_bytes;
+  int stages = norm_stages_override() > 0 ? norm_stages_override() : 2;
+  if (stages > budget / stage_bytes) stages = budget / stage_bytes;
   if (stages < 2) stages = 2;
   if (stages > kMaxStages) stages = kMaxStages;
   a.stages = stages;
@@ -55,10 +79,12 @@ int launch_norm_tma(NormArgs a, cudaStream_t st) {
     (void)cudaGetLastError();
     return ND_ERR_LAUNCH;
   }
-  long long chunks = resident_slots(fn, nt, smem);
+  long long chunks = resident_slots(fn, nt, smem, a.mode == kFwd);
   const long long most = a.rows / RPI > 1 ? a.rows / RPI : 1;  // every chunk holds at least one full group
   if (chunks > most) chunks = most;
   a.n_chunks = static_cast<int>(chunks);
+  a.chunk_base = a.rows / chunks;
+  a.chunk_rem = static_cast<int>(a.rows % chunks);
   a.b_first = a.row_start / a.seq_len;
   a.n_samples = (a.row_start + a.rows - 1) / a.seq_len - a.b_first + 1;
   if (int s = launch_checked(fn, chunks, nt, a, smem, st)) return s;

@@ -33,14 +33,17 @@ struct GroupCursor {
   long long r, r_end;   // next row, end of the chunk (local to the shard)
   long long b, s_end;   // sample of row r, end of that sample clipped to the chunk (local)
   __device__ __forceinline__ bool init(const NormArgs& a) {
-    r = chunk_start(a.rows, a.n_chunks, blockIdx.x);
-    r_end = chunk_start(a.rows, a.n_chunks, blockIdx.x + 1);
+    r = chunk_start(a.chunk_base, a.chunk_rem, blockIdx.x);
+    r_end = chunk_start(a.chunk_base, a.chunk_rem, blockIdx.x + 1);
     if (r >= r_end) return false;
-    enter_sample(a);
+    const unsigned long long g = static_cast<unsigned long long>(a.row_start + r);
+    // the only division of the walk; 32-bit when the global row index allows
+    b = (g >> 32) == 0 ? static_cast<long long>(static_cast<unsigned int>(g) / static_cast<unsigned int>(a.seq_len))
+                       : static_cast<long long>(g / static_cast<unsigned long long>(a.seq_len));
+    clip_sample(a);
     return true;
   }
-  __device__ __forceinline__ void enter_sample(const NormArgs& a) {
-    b = (a.row_start + r) / a.seq_len;
+  __device__ __forceinline__ void clip_sample(const NormArgs& a) {
     const long long e = (b + 1) * a.seq_len - a.row_start;
     s_end = e < r_end ? e : r_end;
   }
@@ -52,7 +55,10 @@ struct GroupCursor {
   __device__ __forceinline__ bool next(const NormArgs& a, int rpi) {
     r += group_rows(rpi);
     if (r >= r_end) return false;
-    if (r == s_end) enter_sample(a);
+    if (r == s_end) {  // the next sample starts here
+      ++b;
+      clip_sample(a);
+    }
     return true;
   }
 };
@@ -78,7 +84,9 @@ __device__ __forceinline__ void pipeline_start(const NormArgs& a, uint64_t* full
     for (int s = 0; s < a.stages; ++s) mbar_init(&full[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  griddep_launch_dependents();
   __syncthreads();
+  griddep_wait();  // nothing above reads global memory; everything below may
   pc_valid = false;
   if (threadIdx.x == 0) {
     pc_valid = pc.init(a);
@@ -103,8 +111,10 @@ __global__ void __maxnreg__(MAXR) norm_fwd_tma(const NormArgs a) {
   unsigned char* buf = dsm + kBarrierBytes;
   __shared__ __align__(16) float red[2][RPI * 32];
   __shared__ __align__(16) float zero16[4];  // what idle lanes of the last warp read instead of a column
+  __shared__ int s_abort;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
   if (tid < 4) zero16[tid] = 0.f;
+  if (tid == 0) s_abort = 0;
 
   const int H = a.hidden;
   const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
@@ -141,11 +151,9 @@ __global__ void __maxnreg__(MAXR) norm_fwd_tma(const NormArgs a) {
     do {
       const long long r = cc.r;
       const int nrows = cc.group_rows(RPI);
-      const bool arrived = mbar_wait_1s(&full[stage], parity, a.err, 1);
-      if (!__syncthreads_and(arrived)) {
-        drain_after_abort();
-        return;
-      }
+      // A wait that expires raises the CTA's abort flag; everybody sees it after the next barrier (the
+      // one inside the row reduction) and the CTA leaves together.
+      if (!mbar_wait_1s(&full[stage], parity, a.err, 1)) s_abort = 1;
       // this thread's 16-byte column of each row (rows past the group's end hold stale data: they are
       // reduced like the others, independently per row, and never stored)
       const unsigned char* src =
@@ -172,6 +180,10 @@ __global__ void __maxnreg__(MAXR) norm_fwd_tma(const NormArgs a) {
         cta_sum_rows_post<1, RPI>(s, mean_mine, red[phase], lane, warp, warps,
                                   [&](int, float t) { return -t * inv_h; });  // broadcast -mean
         phase ^= 1;
+        if (*static_cast<volatile int*>(&s_abort)) {
+          drain_after_abort();
+          return;
+        }
         if (tid == 0 && pc_valid) {  // every thread has read the stage: refill it
           fence_proxy_async_smem();
           issue_group<T, RPI, false>(a, pc, stage, full, buf, row_bytes);
@@ -197,6 +209,10 @@ __global__ void __maxnreg__(MAXR) norm_fwd_tma(const NormArgs a) {
       cta_sum_rows_post<1, RPI>(q, rstd_mine, red[phase], lane, warp, warps,
                                 [&](int, float t) { return rsqrt_newton(fmaf(t, inv_h, eps)); });  // broadcast 1/std
       phase ^= 1;
+      if (*static_cast<volatile int*>(&s_abort)) {
+        drain_after_abort();
+        return;
+      }
       if (!refilled && tid == 0 && pc_valid) {
         fence_proxy_async_smem();
         issue_group<T, RPI, false>(a, pc, stage, full, buf, row_bytes);
@@ -209,9 +225,10 @@ __global__ void __maxnreg__(MAXR) norm_fwd_tma(const NormArgs a) {
       }
       if (active) {
         T* yp = static_cast<T*>(a.y) + r * row_elems + col;
+        const int limit = nrows == RPI ? RPI : nrows;  // a full group stores without per-row tests
 #pragma unroll
         for (int j = 0; j < RPI; ++j) {
-          if (j < nrows) {
+          if (nrows == RPI || j < limit) {
             const float2 r2 = make_float2(q[0][j], q[0][j]);
             float2 out[NP];
 #pragma unroll
@@ -241,8 +258,10 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma(const NormArgs a) {
   unsigned char* buf = dsm + kBarrierBytes;
   __shared__ __align__(16) float red[2][Q * RPI * 32];
   __shared__ __align__(16) float zero16[4];
+  __shared__ int s_abort;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
   if (tid < 4) zero16[tid] = 0.f;
+  if (tid == 0) s_abort = 0;
 
   const int H = a.hidden;
   const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
@@ -284,16 +303,12 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma(const NormArgs a) {
       float rstd[RPI], nmean[RPI];
 #pragma unroll
       for (int j = 0; j < RPI; ++j) {
-        const long long rr = r + (j < nrows ? j : nrows - 1);  // clamped inside the group
+        const long long rr = r + (full_group || j < nrows ? j : nrows - 1);  // clamped inside the group
         rstd[j] = __ldg(a.invstd + rr);
         if constexpr (!RMS) nmean[j] = -__ldg(a.mean + rr);
         else nmean[j] = 0.f;
       }
-      const bool arrived = mbar_wait_1s(&full[stage], parity, a.err, 2);
-      if (!__syncthreads_and(arrived)) {
-        drain_after_abort();
-        return;
-      }
+      if (!mbar_wait_1s(&full[stage], parity, a.err, 2)) s_abort = 1;  // seen by all after the next barrier
       const unsigned char* src =
           active ? buf + static_cast<size_t>(stage) * stage_total + col * sizeof(T) : reinterpret_cast<const unsigned char*>(zero16);
       float2 X[RPI][NP], G[RPI][NP];
@@ -351,6 +366,10 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma(const NormArgs a) {
       } else {
         __syncthreads();  // every thread has read the stage
       }
+      if (*static_cast<volatile int*>(&s_abort)) {
+        drain_after_abort();
+        return;
+      }
       if (tid == 0 && pc_valid) {
         fence_proxy_async_smem();
         issue_group<T, RPI, true>(a, pc, stage, full, buf, row_bytes);
@@ -365,7 +384,7 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma(const NormArgs a) {
           T* dp = static_cast<T*>(a.dx) + r * row_elems + col;
 #pragma unroll
           for (int j = 0; j < RPI; ++j) {
-            if (j < nrows) {
+            if (full_group || j < nrows) {
               const float2 c2v = make_float2(p[Q - 1][j], p[Q - 1][j]), r2 = make_float2(rstd[j], rstd[j]);
               float2 out[NP];
 #pragma unroll

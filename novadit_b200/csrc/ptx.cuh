@@ -46,6 +46,14 @@ __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_
                : "memory");
 }
 
+// Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute may
+// start while its predecessor in the stream is still running; `griddep_wait` blocks until that
+// predecessor has completed and its writes are visible, so it must precede the first read of any
+// global input. `griddep_launch_dependents` lets the successor start early. Both are no-ops for a
+// kernel launched without the attribute.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Orders this thread's earlier generic-proxy accesses to shared memory before later async-proxy
 // (bulk copy) accesses.
 __device__ __forceinline__ void fence_proxy_async_smem() {
