@@ -33,7 +33,8 @@ enum {
   ND_ERR_UNSUPPORTED = -2, /* dtype / size outside what the kernels cover */
   ND_ERR_LAUNCH = -3,      /* CUDA reported an error at launch; see nd_last_cuda_error() */
   ND_ERR_WORKSPACE = -4,   /* workspace missing, too small or misaligned */
-  ND_ERR_DEVICE = -5       /* a bounded device-side wait expired (see the status argument of nd_fc1_fwd) */
+  ND_ERR_DEVICE = -5,      /* a bounded device-side wait expired (see the status argument of nd_fc1_fwd) */
+  ND_ERR_TOO_LARGE = -6    /* the problem needs more scratch than the no-allocation entry point carries */
 };
 
 /* element types. csrc/common/type_dispatch.h:5-6 dispatches on the same set */
@@ -108,6 +109,24 @@ int nd_adaln_bwd(int dtype, const void* dy, const void* x, const void* scale, co
                  const float* invstd, void* dx, float* dscale, float* dshift, int64_t rows,
                  int64_t row_start, int64_t seq_len, int64_t hidden, void* ws, size_t ws_bytes,
                  void* stream);
+
+/* nd_adaln_bwd for callers that cannot provide scratch memory (no counterpart in the reference).
+ * Who needs it: a process that handed all device memory to its own pool at start-up, a plugin whose
+ * host forbids allocations, code inside a stream capture or a latency-critical loop where cudaMalloc
+ * is illegal or stalls the device. The fp32 partial sums of the dparam reduction go through a fixed
+ * array of nd_noalloc_scratch_bytes() (16 MiB) in the library's own device image, which every GPU
+ * that loads the library holds until the process exits; inputs and outputs are still the caller's.
+ * The call allocates nothing and calls no allocating routine. Problems whose
+ * nd_norm_dparam_ws_bytes(...) exceeds the array are refused with ND_ERR_TOO_LARGE (use nd_adaln_bwd
+ * with your own workspace). The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current) and should come before any stream capture. All
+ * calls on a device share the one array: calls whose kernels may overlap on the GPU (different
+ * streams) race on it and must be serialised by the caller. The array keeps the previous call's
+ * contents; nothing in it needs clearing. Same arguments and results as nd_adaln_bwd. */
+size_t nd_noalloc_scratch_bytes(void);
+int nd_adaln_bwd_noalloc(int dtype, const void* dy, const void* x, const void* scale, const float* mean,
+                         const float* invstd, void* dx, float* dscale, float* dshift, int64_t rows,
+                         int64_t row_start, int64_t seq_len, int64_t hidden, void* stream);
 
 /* ------------------------------------------------------------- AdaRMSNorm */
 

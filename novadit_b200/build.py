@@ -42,6 +42,7 @@ CU_SOURCES = [
     "gate_act.cu",
     "quant.cu",
     "fc1.cu",
+    "noalloc.cu",
 ]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -43,6 +43,9 @@ SIGNATURES = {
                                     c_void_p, *_SHAPE4, c_void_p, c_size_t, c_void_p]),
     "nd_adaln_bwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_void_p, c_void_p, *_SHAPE4, c_void_p, c_size_t, c_void_p]),
+    "nd_noalloc_scratch_bytes": (c_size_t, []),
+    "nd_adaln_bwd_noalloc": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, *_SHAPE4, c_void_p]),
     "nd_adarms_fwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, *_SHAPE4,
                               c_float, c_void_p]),
     "nd_adarms_bwd_dx": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, *_SHAPE4,

@@ -61,6 +61,7 @@ const char* nd_status_string(int status) {
     case ND_ERR_LAUNCH: return "CUDA launch failed";
     case ND_ERR_WORKSPACE: return "workspace missing, too small or not 256-byte aligned";
     case ND_ERR_DEVICE: return "a bounded device-side wait expired";
+    case ND_ERR_TOO_LARGE: return "problem too large for the built-in scratch of the no-allocation entry point";
     default: return "unknown status";
   }
 }
