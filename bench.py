@@ -50,9 +50,10 @@ ROWS = B * S
 FWD_BYTES = 2 * ROWS * H * E + 2 * B * H * E + 2 * ROWS * 4                       # 37 961 728
 BWD_BYTES = 3 * ROWS * H * E + B * H * E + 2 * ROWS * 4 + 2 * B * H * 4           # 57 057 280
 STEP_BYTES = FWD_BYTES + BWD_BYTES                                                # 95 019 008
-# DRAM traffic per launch of the dominant kernel measured by ncu (dram__bytes_read + write), filled in
-# from profiles/ once a capture exists; None = not captured.
-NCU_TRAFFIC_BWD = None
+# DRAM traffic per launch of the dominant kernel measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum
+# of norm_bwd_tma at this shape, profiles/norm_config2_adaln.md): 37 915 392 B read + 258 560 B written. The
+# 18.9 MB of dx is still dirty in L2 when the kernel ends, hence traffic < algorithmic bytes.
+NCU_TRAFFIC_BWD = 38173952
 
 
 def measured_peaks() -> tuple[float, float, str]:
@@ -418,7 +419,7 @@ def run_gpu_arm(args) -> None:
                        "global_rows": world * ROWS, "parallelism": f"rows sharded over {world} GPU(s), no collective",
                        "cold_cache": f"{NSETS} rotating buffer sets (605 MB > 4x L2)", "launch": "CUDA graphs"},
             "frac_of_hbm_peak": value / world / hbm_peak,
-            "roofline": {"kernel": "norm_bwd_kernel (dx + dscale/dshift, one pass)", "bound": "hbm",
+            "roofline": {"kernel": "norm_bwd_tma + norm_dparam_stage2 (dx + dscale/dshift, one pass over dy and x)", "bound": "hbm",
                          "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": NCU_TRAFFIC_BWD, "peak_source": peak_src, "algorithmic_bytes": BWD_BYTES,
                          "avg_launch_ms": bwd_ms},

@@ -1,9 +1,10 @@
 // Fused FC1: y = epilogue((x @ w^T) * alpha + bias) on the 5th-generation tensor cores (sm_100a).
 //
-// One persistent CTA per SM, 192 threads, warp-specialised:
+// One persistent CTA per SM, 320 threads, warp-specialised:
 //   warp 0      TMA producer: x and w tiles -> 128B-swizzled shared memory, 4-stage mbarrier ring
 //   warp 1      tcgen05.mma issuer (one lane) + owner of the tensor-memory allocation
-//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator, * alpha, + bias, activation
+//   warps 2..9  epilogue (two warps per TMEM lane quarter, each taking half of the tile's columns):
+//               tcgen05.ld the fp32 accumulator, * alpha, + bias, activation
 //               (gated: value * act(gate)), round once, 64-byte row segments to global memory
 // CTA tile: 128 rows x 256 accumulator columns x 128 bytes of K per stage. For the gated form
 // the 256 columns are 128 gate columns and the 128 value columns of the SAME output columns,
@@ -29,7 +30,8 @@ constexpr int kBM = 128;         // rows per CTA tile
 constexpr int kBN = 256;         // accumulator columns per CTA tile
 constexpr int kBKBytes = 128;    // bytes of K per stage = one 128B swizzle span
 constexpr int kStages = 4;
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kATileBytes = kBM * kBKBytes;          // 16 KB
 constexpr int kBHalfBytes = 128 * kBKBytes;          // 16 KB (128 weight rows)
 constexpr int kStageBytes = kATileBytes + 2 * kBHalfBytes;  // 48 KB
@@ -50,7 +52,7 @@ struct Fc1Args {
 
 struct __align__(1024) Fc1Smem {
   uint8_t stage[kStages][kStageBytes];
-  float bias[4][kBN];  // one private copy per epilogue warp: no cross-warp barrier in the epilogue
+  float bias[kEpilogueWarps][kBN];  // one private copy per epilogue warp: no cross-warp barrier in the epilogue
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t tmem_full[2];
@@ -184,7 +186,7 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.tmem_full[i], 1);
-      mbar_init(&s.tmem_empty[i], 4);
+      mbar_init(&s.tmem_empty[i], kEpilogueWarps);
     }
     s.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -279,6 +281,7 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
   } else {
     // ---------------------------------------------------------------- epilogue (4 warps)
     const int q = warp & 3;             // TMEM lane quarter this warp may read
+    const int colhalf = (warp - 2) >> 2;   // which half of the tile's column steps this warp takes
     int acc = 0;
     uint32_t acc_phase = 0;
     float alpha = a.alpha_host;
@@ -291,7 +294,7 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
       tile_coords(a, t, mi, ni);
       const int out0 = GATED != 0 ? ni * 128 : ni * kBN;  // first output column of the tile
       // bias of the tile's 256 accumulator columns -> this warp's shared-memory copy (fp32)
-      float* sb = s.bias[q];
+      float* sb = s.bias[warp - 2];
 #pragma unroll
       for (int h = 0; h < kBN / 32; ++h) {
         const int c = lane + h * 32;
@@ -311,7 +314,7 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
       constexpr int kSteps = GATED == 1 ? 4 : 8;
       constexpr int kOutPer = GATED == 2 ? 16 : 32;
 #pragma unroll 1
-      for (int ch = 0; ch < kSteps; ++ch) {
+      for (int ch = colhalf * (kSteps / 2); ch < (colhalf + 1) * (kSteps / 2); ++ch) {
         float out[kOutPer];
         if constexpr (GATED == 1) {
           float g[32], v[32];
