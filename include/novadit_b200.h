@@ -189,6 +189,15 @@ int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const void* x, c
                const void* bias, float alpha_host, const float* alpha_dev, void* y, int64_t m,
                int64_t k, int64_t n, int* status, void* stream);
 
+/* Tuning hook: 1 = two-CTA tiles (tcgen05 cta_group::2 over clusters of two CTAs), 0 = single-CTA
+ * tiles, negative (default) = chosen per problem. Process-wide. No counterpart in the reference. */
+void nd_tune_fc1_pair(int mode);
+/* Diagnostic hook: a device array of 8 int64 that later nd_fc1_fwd launches add cycle counters to
+ * ([0] copy thread waiting for a free stage, [3]/[4] one epilogue warp waiting / working, [5]/[7] the
+ * copy thread's lifetime in cycles / nanoseconds); NULL (default) turns it off. No counterpart in the
+ * reference. */
+void nd_tune_fc1_trace(long long* device_counters);
+
 /* amax = max |x| over n elements (fp32 result, device). Two-stage and deterministic:
  * `ws` holds per-CTA maxima; nd_amax_ws_bytes() bytes, 256-byte aligned. No counterpart in
  * the reference (it has no FP8 path). */

@@ -167,24 +167,36 @@ __device__ __forceinline__ void cta_sum_rows(float (&v)[Q][N], float* red, int l
   }
 }
 
-// x * sigmoid(t): the common form of SiLU (t = x) and tanh-GELU (t = 2u), with
-// sigmoid from exp2f and a 2-ulp reciprocal so that the value before the output
-// rounding stays within ~1e-6 relative of the exact one (tanh.approx, at 5e-4
-// absolute, would flip output roundings against the fp32 reference).
-__device__ __forceinline__ float sigmoid_f32(float t) {
-  return __fdividef(1.f, 1.f + exp2f(-1.4426950408889634f * t));
+// x * sigmoid(t): the common form of SiLU (t = x) and tanh-GELU (t = 2u). sigmoid = 1 / (1 + 2^(-t log2 e))
+// from the two special-function instructions directly (ex2.approx: 2 ulp, rcp.approx: 1 ulp; flush-to-zero,
+// +inf -> 0), so that the value before the output rounding stays within ~1e-6 relative of the exact one
+// (tanh.approx, at 5e-4 absolute, would flip output roundings against the fp32 reference). Four instructions
+// per sigmoid; the library exp2f / division would add range fix-ups that the formula does not need.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 1 / (1 + 2^e)
+__device__ __forceinline__ float sigmoid_from_exp2arg(float e) { return rcp_approx(1.f + ex2_approx(e)); }
+__device__ __forceinline__ float sigmoid_f32(float t) { return sigmoid_from_exp2arg(-1.4426950408889634f * t); }
 
 constexpr float kGeluC0 = 0.7978845608028654f;  // sqrt(2/pi)
 constexpr float kGeluC1 = 0.044715f;
+// tanh-GELU: 0.5 g (1 + tanh u) == g * sigmoid(2u), u = c0 (g + c1 g^3); exponent argument -2 log2(e) u
+constexpr float kGeluE0 = -2.f * 1.4426950408889634f * kGeluC0;
+constexpr float kGeluE1 = kGeluE0 * kGeluC1;
 
 template <int ACT> __device__ __forceinline__ float act_fwd(float g) {
   if constexpr (ACT == ND_ACT_SILU) {
     return g * sigmoid_f32(g);
   } else {
-    // 0.5 g (1 + tanh u) == g * sigmoid(2u)
-    const float u = kGeluC0 * (g + kGeluC1 * g * g * g);
-    return g * sigmoid_f32(2.f * u);
+    return g * sigmoid_from_exp2arg(g * fmaf(kGeluE1, g * g, kGeluE0));
   }
 }
 
@@ -196,8 +208,7 @@ template <int ACT> __device__ __forceinline__ float act_fwd_grad(float g, float&
     return g * s;
   } else {
     const float g2 = g * g;
-    const float u = kGeluC0 * (g + kGeluC1 * g * g2);
-    const float s = sigmoid_f32(2.f * u);  // = 0.5 (1 + tanh u)
+    const float s = sigmoid_from_exp2arg(g * fmaf(kGeluE1, g2, kGeluE0));  // = 0.5 (1 + tanh u)
     // d/dg [g s] = s + g * s' ,  s' = 2 s (1 - s) * du/dg
     const float du = kGeluC0 * (1.f + 3.f * kGeluC1 * g2);
     grad = s + g * 2.f * s * (1.f - s) * du;

@@ -11,7 +11,7 @@
 // staged as one K-major B operand (gate rows then value rows), so a single UMMA of N=256
 // produces both halves and the epilogue combines TMEM columns c and 128+c. Two accumulators
 // (2 x 256 of the 512 TMEM columns) let the epilogue of tile i overlap the main loop of tile
-// i+1. No cluster, no multicast: every CTA issues its own TMA loads.
+// i+1. No cluster: every CTA issues its own TMA loads.
 //
 // Every wait on an mbarrier is bounded (1 s of %globaltimer); on expiry the waiting role raises
 // a CTA-wide abort flag, the status word in global memory is set, every role leaves its loop,
@@ -19,6 +19,7 @@
 #include <cuda.h>
 #include <cuda_fp8.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -36,6 +37,7 @@ constexpr int kATileBytes = kBM * kBKBytes;          // 16 KB
 constexpr int kBHalfBytes = 128 * kBKBytes;          // 16 KB (128 weight rows)
 constexpr int kStageBytes = kATileBytes + 2 * kBHalfBytes;  // 48 KB
 constexpr int kTmemCols = 512;
+constexpr int kOutBlockBytes = 32 * 32 * 2;  // 32 rows x 32 output columns of a 16-bit type
 constexpr int kGroupM = 8;       // tile rasterisation: m-blocks per group
 constexpr unsigned long long kWaitLimitNs = 1000000000ull;
 
@@ -44,6 +46,7 @@ struct Fc1Args {
   void* y;
   const float* alpha_dev;  // nullable, two floats multiplied into alpha
   int* status;             // nullable
+  long long* trace;        // nullable: per-role cycle counters (see nd_tune_fc1_trace)
   float alpha_host;
   int m, k, n;             // n = rows of w
   int n_out;               // columns of y (n/2 gated, n plain)
@@ -52,7 +55,8 @@ struct Fc1Args {
 
 struct __align__(1024) Fc1Smem {
   uint8_t stage[kStages][kStageBytes];
-  float bias[kEpilogueWarps][kBN];  // one private copy per epilogue warp: no cross-warp barrier in the epilogue
+  uint8_t out[kEpilogueWarps][kOutBlockBytes];  // output staging, one 32 x 32 block per epilogue warp
+  alignas(16) float bias[kEpilogueWarps][kBN];  // one private copy per epilogue warp: no cross-warp barrier in the epilogue
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t tmem_full[2];
@@ -79,6 +83,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// mbar_wait that also adds the cycles spent waiting to a per-role counter (lane 0 only; `acc` may be null)
+__device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                int code, long long* acc) {
+  if (acc == nullptr) return mbar_wait(bar, parity, abort_flag, status, code);
+  const long long t0 = clock64();
+  const bool ok = mbar_wait(bar, parity, abort_flag, status, code);
+  *acc += clock64() - t0;
+  return ok;
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0,
                                             int c1) {
   asm volatile(
@@ -90,30 +104,6 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-
-template <bool F8>
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
-  if constexpr (F8) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  }
-}
-
-// 32 consecutive fp32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&r)[32]) {
   uint32_t* u = reinterpret_cast<uint32_t*>(r);
   asm volatile(
@@ -166,12 +156,208 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Bias of the tile's 256 accumulator columns -> one epilogue warp's shared-memory copy (fp32).
+template <int GATED, typename OUT>
+__device__ __forceinline__ void stage_bias(const Fc1Args& a, float* sb, int ni, int lane) {
+  const OUT* __restrict__ bias = static_cast<const OUT*>(a.bias);
+  const int out0 = GATED != 0 ? ni * 128 : ni * kBN;
+#pragma unroll
+  for (int h = 0; h < kBN / 32; ++h) {
+    const int c = lane + h * 32;
+    int wrow;  // row of w (= index into bias) behind accumulator column c
+    if (GATED == 1) wrow = (c < 128) ? (out0 + c) : (a.n_out + out0 + c - 128);
+    else wrow = ni * kBN + c;
+    const bool in = GATED == 1 ? (out0 + (c & 127) < a.n_out) : (wrow < a.n);
+    sb[c] = (bias != nullptr && in) ? to_f32(bias[wrow]) : 0.f;
+  }
+  __syncwarp();
+}
+
+// 2-D bulk-tensor store of one 32-row x 32-column output block (64-byte rows, 64-byte swizzle) from shared
+// memory; rows and columns outside the tensor are clipped by the copy engine.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the issuing thread's earlier bulk stores have finished READING shared memory
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... and have completed
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// One epilogue warp's share of a finished tile: its 32 rows (TMEM lanes at `t_lane`, first row `row0`), half of
+// the tile's column steps (`colhalf`). z = acc * alpha + bias, activation, gating, one rounding. Each step
+// yields 32 output columns per row; the warp writes them into its 2 KB staging block (row = lane, 16-byte
+// chunk c of row r at chunk c ^ ((r >> 1) & 3): the 64-byte swizzle, free of bank conflicts) and one lane hands
+// the block to the copy engine. A thread writing its own row straight to global memory costs the L1 one tag
+// lookup per row and instruction (32 per store instruction), which made the stores the longest part of the
+// epilogue; the bulk store writes whole 64-byte row segments and costs the warp one instruction.
+template <int GATED, int ACT, typename OUT>
+__device__ __forceinline__ void epilogue_columns(const Fc1Args& a, const CUtensorMap* map_y, const float* sb,
+                                                 uint8_t* obuf, uint32_t t_lane, int row0, int ni, int colhalf,
+                                                 float alpha, int lane) {
+  const int out0 = GATED != 0 ? ni * 128 : ni * kBN;  // first output column of the tile
+  constexpr int kSteps = GATED != 0 ? 4 : 8;          // steps of 32 output columns per tile
+  // bias values come from shared memory four at a time (all lanes read the same address)
+  const float4* sb4 = reinterpret_cast<const float4*>(sb);
+#pragma unroll 1
+  for (int ch = colhalf * (kSteps / 2); ch < (colhalf + 1) * (kSteps / 2); ++ch) {
+    float out[32];
+    if constexpr (GATED == 1) {
+      float g[32], v[32];
+      tc_ld32(t_lane + ch * 32, g);
+      tc_ld32(t_lane + 128 + ch * 32, v);
+      tc_wait_ld();
+#pragma unroll
+      for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 bg = sb4[ch * 8 + j4], bv = sb4[32 + ch * 8 + j4];
+        const float bgs[4] = {bg.x, bg.y, bg.z, bg.w}, bvs[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = j4 * 4 + e;
+          out[j] = fmaf(v[j], alpha, bvs[e]) * act_fwd<ACT>(fmaf(g[j], alpha, bgs[e]));
+        }
+      }
+    } else if constexpr (GATED == 2) {
+      float z0[32], z1[32];  // accumulator columns (gate, value, gate, ...) of output columns 0..15 and 16..31
+      tc_ld32(t_lane + ch * 64, z0);
+      tc_ld32(t_lane + ch * 64 + 32, z1);
+      tc_wait_ld();
+#pragma unroll
+      for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 b0 = sb4[ch * 16 + j4], b1 = sb4[ch * 16 + 8 + j4];
+        out[2 * j4] = fmaf(z0[4 * j4 + 1], alpha, b0.y) * act_fwd<ACT>(fmaf(z0[4 * j4], alpha, b0.x));
+        out[2 * j4 + 1] = fmaf(z0[4 * j4 + 3], alpha, b0.w) * act_fwd<ACT>(fmaf(z0[4 * j4 + 2], alpha, b0.z));
+        out[16 + 2 * j4] = fmaf(z1[4 * j4 + 1], alpha, b1.y) * act_fwd<ACT>(fmaf(z1[4 * j4], alpha, b1.x));
+        out[16 + 2 * j4 + 1] = fmaf(z1[4 * j4 + 3], alpha, b1.w) * act_fwd<ACT>(fmaf(z1[4 * j4 + 2], alpha, b1.z));
+      }
+    } else {
+      float z[32];
+      tc_ld32(t_lane + ch * 32, z);
+      tc_wait_ld();
+#pragma unroll
+      for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 b = sb4[ch * 8 + j4];
+        out[4 * j4 + 0] = act_fwd<ACT>(fmaf(z[4 * j4 + 0], alpha, b.x));
+        out[4 * j4 + 1] = act_fwd<ACT>(fmaf(z[4 * j4 + 1], alpha, b.y));
+        out[4 * j4 + 2] = act_fwd<ACT>(fmaf(z[4 * j4 + 2], alpha, b.z));
+        out[4 * j4 + 3] = act_fwd<ACT>(fmaf(z[4 * j4 + 3], alpha, b.w));
+      }
+    }
+    if (lane == 0) bulk_wait_read_all();  // the previous block has left the staging memory
+    __syncwarp();
+    const int sw = (lane >> 1) & 3;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint4 pk;
+      pk.x = pack2<OUT>(out[c * 8 + 0], out[c * 8 + 1]);
+      pk.y = pack2<OUT>(out[c * 8 + 2], out[c * 8 + 3]);
+      pk.z = pack2<OUT>(out[c * 8 + 4], out[c * 8 + 5]);
+      pk.w = pack2<OUT>(out[c * 8 + 6], out[c * 8 + 7]);
+      *reinterpret_cast<uint4*>(obuf + lane * 64 + ((c ^ sw) << 4)) = pk;
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    const int col = out0 + ch * 32;
+    if (lane == 0 && row0 < a.m && col < a.n_out) {
+      tma_store_2d(map_y, obuf, col, row0);
+      bulk_commit();
+    }
+  }
+}
+
+// ------------------------------------------------------------------ the MMA issuer
+// tcgen05.mma with the operand descriptors given as (low word, shared high word): only the 14-bit start
+// address in the low word differs between stages and K slices, so the issuing thread keeps one register per
+// operand and adds compile-time constants.
+template <bool F8, bool PAIR>
+__device__ __forceinline__ void tc_mma_split(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                             uint32_t accumulate) {
+#define ND_MMA_ASM(GROUP, KIND)                                                                                     \
+  asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tmov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"       \
+               "setp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], da, db, %3, p;\n\t}" \
+               ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(hi)                             \
+               : "memory")
+  if constexpr (PAIR) {
+    if constexpr (F8) ND_MMA_ASM("2", "f8f6f4");
+    else ND_MMA_ASM("2", "f16");
+  } else {
+    if constexpr (F8) ND_MMA_ASM("1", "f8f6f4");
+    else ND_MMA_ASM("1", "f16");
+  }
+#undef ND_MMA_ASM
+}
+
+// "all MMAs issued so far have completed" -> one arrival on `bar`; for a CTA pair, on that barrier in both CTAs
+template <bool PAIR> __device__ __forceinline__ void tc_commit_to(uint64_t* bar) {
+  if constexpr (PAIR) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(static_cast<uint16_t>(3))
+                 : "memory");
+  } else {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+  }
+}
+
+// The whole MMA stream of one CTA (or CTA pair), run by ONE thread: `my_tiles` tiles of `k_blocks` stages each.
+// The tensor pipe only stays busy if this thread issues one MMA per ~128 cycles while the epilogue warps of the
+// same scheduler compete for issue slots, so the loop is kept to the bare chain: the stage ring is unrolled
+// (barrier and operand addresses are constants), the operand descriptors are one add away, and the barrier of
+// the NEXT stage is polled before the current stage's MMAs are issued so that its answer is there when needed.
+template <bool F8, bool PAIR, int STAGES, int STAGE_BYTES>
+__device__ __forceinline__ void mma_issue_loop(uint32_t stage0_addr, uint64_t* full, uint64_t* empty,
+                                               uint64_t* tmem_full, uint64_t* tmem_empty, uint32_t tmem_base,
+                                               uint32_t idesc, int my_tiles, int k_blocks, volatile int* abort_flag,
+                                               int* status, int code_tmem, int code_full) {
+  const uint32_t a_lo0 = static_cast<uint32_t>(umma_desc(stage0_addr));
+  const uint32_t b_lo0 = static_cast<uint32_t>(umma_desc(stage0_addr + kATileBytes));
+  const uint32_t hi = static_cast<uint32_t>(umma_desc(stage0_addr) >> 32);
+  const long long total_it = static_cast<long long>(my_tiles) * k_blocks;
+  int kb = 0, acc = 0;
+  uint32_t phase = 0, acc_phase = 0;
+  bool ok = true;
+  bool ready = total_it > 0 && mbar_try_wait(&full[0], 0);
+  for (long long it0 = 0; it0 < total_it && ok; it0 += STAGES) {
+#pragma unroll
+    for (int st = 0; st < STAGES; ++st) {
+      if (it0 + st >= total_it) break;
+      if (kb == 0) {  // first stage of a tile: its accumulator must have been drained by the epilogue
+        ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, status, code_tmem);
+        if (!ok) break;
+      }
+      if (!ready) {
+        ok = mbar_wait(&full[st], phase, abort_flag, status, code_full);
+        if (!ok) break;
+      }
+      tc_fence_after();
+      const int nst = (st + 1) % STAGES;  // the ring is unrolled: st, nst and `so` below fold to constants
+      ready = (it0 + st + 1 < total_it) && mbar_try_wait(&full[nst], st + 1 == STAGES ? phase ^ 1u : phase);
+      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kBN);
+      const uint32_t so = static_cast<uint32_t>(st) * (STAGE_BYTES >> 4);  // descriptor addresses count 16 bytes
+      tc_mma_split<F8, PAIR>(d_tmem, a_lo0 + so, b_lo0 + so, hi, idesc, kb != 0 ? 1u : 0u);
+#pragma unroll
+      for (int kk = 1; kk < kBKBytes / 32; ++kk)  // +32 bytes of K inside the swizzle span = +2 address units
+        tc_mma_split<F8, PAIR>(d_tmem, a_lo0 + so + 2u * kk, b_lo0 + so + 2u * kk, hi, idesc, 1u);
+      tc_commit_to<PAIR>(&empty[st]);  // the stage is free again once these MMAs have read it
+      if (++kb == k_blocks) {
+        tc_commit_to<PAIR>(&tmem_full[acc]);  // accumulator complete
+        kb = 0;
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+    phase ^= 1u;
+  }
+}
+
 // ABF: instruction-descriptor operand format (kind::f16: 0 = f16, 1 = bf16; kind::f8f6f4: 0 = e4m3)
 // GATED: 0 = y = act(z); 1 = w rows [gate block | value block]; 2 = w rows interleaved (gate0, value0, gate1, ...)
 template <bool F8, int ABF, int GATED, int ACT, typename OUT>
 __global__ void __launch_bounds__(kThreads, 1)
 fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-           const Fc1Args a) {
+           const __grid_constant__ CUtensorMap map_y, const Fc1Args a) {
   extern __shared__ uint8_t smem_raw[];
   Fc1Smem& s = *reinterpret_cast<Fc1Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -205,165 +391,92 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
   const uint32_t tmem_base = s.tmem_base;
 
   if (warp == 0) {
-    // ---------------------------------------------------------------- TMA producer
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      int mi, ni;
-      tile_coords(a, t, mi, ni);
-      const int m0 = mi * kBM;
-      // stacked gating: gate rows [n0, n0+128) and value rows [n_out + n0, ...); otherwise rows [n0, n0+256)
-      const int nb0 = GATED == 1 ? ni * 128 : ni * kBN;
-      const int nb1 = GATED == 1 ? a.n_out + ni * 128 : ni * kBN + 128;
-      for (int kb = 0; kb < a.k_blocks; ++kb) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag, a.status, 1));
-        if (!ok) break;
-        if (lane == 0) {
+    // ---------------------------------------------------------------- TMA producer (one thread)
+    if (lane == 0) {
+      long long w_empty = 0;
+      long long* tr0 = a.trace != nullptr ? &w_empty : nullptr;
+      const long long t_start = clock64();
+      const unsigned long long ns_start = global_ns();
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int mi, ni;
+        tile_coords(a, t, mi, ni);
+        const int m0 = mi * kBM;
+        // stacked gating: gate rows [n0, n0+128) and value rows [n_out + n0, ...); otherwise rows [n0, n0+256)
+        const int nb0 = GATED == 1 ? ni * 128 : ni * kBN;
+        const int nb1 = GATED == 1 ? a.n_out + ni * 128 : ni * kBN + 128;
+        for (int kb = 0; kb < a.k_blocks; ++kb) {
+          ok = mbar_wait_timed(&s.empty[stage], phase ^ 1u, abort_flag, a.status, 1, tr0);
+          if (!ok) break;
           mbar_expect_tx(&s.full[stage], kStageBytes);
           uint8_t* base = s.stage[stage];
           tma_load_2d(base, &map_x, &s.full[stage], kb * kBKElems, m0);
           tma_load_2d(base + kATileBytes, &map_w, &s.full[stage], kb * kBKElems, nb0);
           tma_load_2d(base + kATileBytes + kBHalfBytes, &map_w, &s.full[stage], kb * kBKElems, nb1);
-        }
-        __syncwarp();
-        if (++stage == kStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
-      }
-    }
-    if (!ok) {
-      // let copies already issued land in shared memory before the CTA may exit
-      const unsigned long long t0 = global_ns();
-      while (global_ns() - t0 < 200000ull) __nanosleep(1000);
-    }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
-    int stage = 0;
-    uint32_t phase = 0;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    constexpr uint32_t idesc = umma_idesc(ABF);
-    bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      ok = __all_sync(0xffffffffu, mbar_wait(&s.tmem_empty[acc], acc_phase ^ 1u, abort_flag, a.status, 2));
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kBN);
-      for (int kb = 0; kb < a.k_blocks; ++kb) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&s.full[stage], phase, abort_flag, a.status, 3));
-        if (!ok) break;
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t a_addr = smem_u32(s.stage[stage]);
-          const uint64_t da = umma_desc(a_addr);
-          const uint64_t db = umma_desc(a_addr + kATileBytes);
-#pragma unroll
-          for (int kk = 0; kk < kBKBytes / 32; ++kk) {
-            // advance 32 bytes of K inside the swizzle span: +2 in 16-byte address units
-            tc_mma<F8>(d_tmem, da + 2ull * kk, db + 2ull * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
           }
-          tc_commit(&s.empty[stage]);  // the stage is free again once these MMAs have read it
-        }
-        __syncwarp();
-        if (++stage == kStages) {
-          stage = 0;
-          phase ^= 1u;
         }
       }
-      if (!ok) break;
-      if (lane == 0) tc_commit(&s.tmem_full[acc]);
-      __syncwarp();
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
+      if (tr0 != nullptr) {
+        atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 0), static_cast<unsigned long long>(w_empty));
+        atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 5), static_cast<unsigned long long>(clock64() - t_start));
+        atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 7), global_ns() - ns_start);
+      }
+      if (!ok) {
+        // let copies already issued land in shared memory before the CTA may exit
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
     }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (one thread)
+    if (lane == 0) {
+      const int my_tiles =
+          static_cast<int>(blockIdx.x) < total_tiles ? (total_tiles - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1 : 0;
+      mma_issue_loop<F8, false, kStages, kStageBytes>(smem_u32(s.stage[0]), s.full, s.empty, s.tmem_full, s.tmem_empty,
+                                                       tmem_base, umma_idesc(ABF), my_tiles, a.k_blocks, abort_flag,
+                                                       a.status, 2, 3);
+    }
+    __syncwarp();
   } else {
-    // ---------------------------------------------------------------- epilogue (4 warps)
+    // ---------------------------------------------------------------- epilogue (8 warps)
     const int q = warp & 3;             // TMEM lane quarter this warp may read
     const int colhalf = (warp - 2) >> 2;   // which half of the tile's column steps this warp takes
+    long long w_tfull = 0, busy = 0;
+    long long* tr3 = (a.trace != nullptr && lane == 0 && warp == 2) ? &w_tfull : nullptr;
     int acc = 0;
     uint32_t acc_phase = 0;
     float alpha = a.alpha_host;
     if (a.alpha_dev != nullptr) alpha *= __ldg(a.alpha_dev) * __ldg(a.alpha_dev + 1);
-    const OUT* __restrict__ bias = static_cast<const OUT*>(a.bias);
-    OUT* __restrict__ y = static_cast<OUT*>(a.y);
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int mi, ni;
       tile_coords(a, t, mi, ni);
-      const int out0 = GATED != 0 ? ni * 128 : ni * kBN;  // first output column of the tile
-      // bias of the tile's 256 accumulator columns -> this warp's shared-memory copy (fp32)
       float* sb = s.bias[warp - 2];
-#pragma unroll
-      for (int h = 0; h < kBN / 32; ++h) {
-        const int c = lane + h * 32;
-        int wrow;  // row of w (= index into bias) behind accumulator column c
-        if (GATED == 1) wrow = (c < 128) ? (out0 + c) : (a.n_out + out0 + c - 128);
-        else wrow = ni * kBN + c;
-        const bool in = GATED == 1 ? (out0 + (c & 127) < a.n_out) : (wrow < a.n);
-        sb[c] = (bias != nullptr && in) ? to_f32(bias[wrow]) : 0.f;
-      }
-      __syncwarp();
-      ok = __all_sync(0xffffffffu, mbar_wait(&s.tmem_full[acc], acc_phase, abort_flag, a.status, 4));
+      stage_bias<GATED, OUT>(a, sb, ni, lane);
+      ok = __all_sync(0xffffffffu, mbar_wait_timed(&s.tmem_full[acc], acc_phase, abort_flag, a.status, 4, tr3));
+      const long long t_busy0 = tr3 != nullptr ? clock64() : 0;
       if (!ok) break;
       tc_fence_after();
-      const int row = mi * kBM + q * 32 + lane;
+      const int row0 = mi * kBM + q * 32;
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * kBN);
-      // per step: kOutPer output columns of this thread's row (a whole number of 16-byte stores)
-      constexpr int kSteps = GATED == 1 ? 4 : 8;
-      constexpr int kOutPer = GATED == 2 ? 16 : 32;
-#pragma unroll 1
-      for (int ch = colhalf * (kSteps / 2); ch < (colhalf + 1) * (kSteps / 2); ++ch) {
-        float out[kOutPer];
-        if constexpr (GATED == 1) {
-          float g[32], v[32];
-          tc_ld32(t_lane + ch * 32, g);
-          tc_ld32(t_lane + 128 + ch * 32, v);
-          tc_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float zg = fmaf(g[j], alpha, sb[ch * 32 + j]);
-            const float zv = fmaf(v[j], alpha, sb[128 + ch * 32 + j]);
-            out[j] = zv * act_fwd<ACT>(zg);
-          }
-        } else if constexpr (GATED == 2) {
-          float z[32];
-          tc_ld32(t_lane + ch * 32, z);
-          tc_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float zg = fmaf(z[2 * j], alpha, sb[ch * 32 + 2 * j]);
-            const float zv = fmaf(z[2 * j + 1], alpha, sb[ch * 32 + 2 * j + 1]);
-            out[j] = zv * act_fwd<ACT>(zg);
-          }
-        } else {
-          float z[32];
-          tc_ld32(t_lane + ch * 32, z);
-          tc_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) out[j] = act_fwd<ACT>(fmaf(z[j], alpha, sb[ch * 32 + j]));
-        }
-        if (row < a.m) {
-          OUT* dst = y + static_cast<long long>(row) * a.n_out + out0 + ch * kOutPer;
-#pragma unroll
-          for (int v8 = 0; v8 < kOutPer / 8; ++v8) {
-            if (out0 + ch * kOutPer + v8 * 8 < a.n_out) {  // n_out is a multiple of 8
-              uint4 pk;
-              pk.x = pack2<OUT>(out[v8 * 8 + 0], out[v8 * 8 + 1]);
-              pk.y = pack2<OUT>(out[v8 * 8 + 2], out[v8 * 8 + 3]);
-              pk.z = pack2<OUT>(out[v8 * 8 + 4], out[v8 * 8 + 5]);
-              pk.w = pack2<OUT>(out[v8 * 8 + 6], out[v8 * 8 + 7]);
-              *reinterpret_cast<uint4*>(dst + v8 * 8) = pk;
-            }
-          }
-        }
-      }
+      epilogue_columns<GATED, ACT, OUT>(a, &map_y, sb, s.out[warp - 2], t_lane, row0, ni, colhalf, alpha, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.tmem_empty[acc]);
+      if (tr3 != nullptr) busy += clock64() - t_busy0;
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
+    }
+    if (lane == 0) bulk_wait_all();  // this warp's output blocks are written before the CTA may exit
+    if (tr3 != nullptr) {
+      atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 3), static_cast<unsigned long long>(w_tfull));
+      atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 4), static_cast<unsigned long long>(busy));
     }
   }
 
@@ -372,6 +485,207 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
   tc_fence_after();
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ two-CTA tiles (cta_group::2)
+// A cluster of two CTAs on neighbouring SMs computes a 256 x 256 accumulator tile with one UMMA stream
+// issued by the leader (cluster rank 0): each CTA stages the 128 A rows it owns and HALF of the B tile
+// (128 weight rows), the tensor cores of both SMs read both halves, and each CTA's tensor memory
+// receives the accumulator rows it owns. Per SM that is 32 KB of operands per 128 bytes of K instead
+// of 48 KB, which is what the single-CTA kernel runs short of. No multicast loads: every CTA copies
+// its own tiles; completion bytes of both CTAs are counted on the leader's mbarrier, and the
+// leader's tcgen05.commit signals the "stage free" and "accumulator ready" barriers of both CTAs.
+constexpr int kPairStages = 6;
+constexpr int kPairStageBytes = kATileBytes + kBHalfBytes;  // 32 KB per CTA and stage
+
+struct __align__(1024) Fc1PairSmem {
+  uint8_t stage[kPairStages][kPairStageBytes];
+  uint8_t out[kEpilogueWarps][kOutBlockBytes];
+  alignas(16) float bias[kEpilogueWarps][kBN];
+  uint64_t full[kPairStages];    // used in the leader only: bytes of both CTAs land here
+  uint64_t empty[kPairStages];   // in each CTA: signalled by the leader's commit
+  uint64_t tmem_full[2];         // in each CTA: signalled by the leader's commit
+  uint64_t tmem_empty[2];        // used in the leader only: the epilogue warps of both CTAs arrive here
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_count_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `local` (a shared::cta address) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 2-D tiled copy into this CTA's shared memory whose completion bytes are counted on an mbarrier that
+// may live in the other CTA of the pair (`bar_cluster_addr` is a shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0,
+                                                 int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+// dense MMA over the CTA pair: M = 256 (128 rows per CTA), N = 256, fp32 accumulator, K-major operands
+__host__ __device__ constexpr uint32_t umma_idesc_pair(uint32_t ab_format) {
+  return (1u << 4) | (ab_format << 7) | (ab_format << 10) | ((kBN >> 3) << 17) | ((256u >> 4) << 24);
+}
+
+// tile t of the pair grid -> (256-row block, n tile); same grouped order as the single-CTA kernel
+__device__ __forceinline__ void pair_tile_coords(int tiles_m2, int tiles_n, int t, int& mi, int& ni) {
+  const int per_group = kGroupM * tiles_n;
+  const int g = t / per_group;
+  const int first_m = g * kGroupM;
+  const int gm = (tiles_m2 - first_m) < kGroupM ? (tiles_m2 - first_m) : kGroupM;
+  const int r = t - g * per_group;
+  mi = first_m + r % gm;
+  ni = r / gm;
+}
+
+template <bool F8, int ABF, int GATED, int ACT, typename OUT>
+__global__ void __launch_bounds__(kThreads, 1)
+fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                const __grid_constant__ CUtensorMap map_y, const Fc1Args a) {
+  extern __shared__ uint8_t smem_raw[];
+  Fc1PairSmem& s = *reinterpret_cast<Fc1PairSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &s.abort_flag;
+  constexpr int kBKElems = F8 ? 128 : 64;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int tiles_m2 = (a.m + 2 * kBM - 1) / (2 * kBM);
+  const int total_tiles = tiles_m2 * a.tiles_n;
+  const int first_tile = static_cast<int>(cluster_id_x()), tile_step = static_cast<int>(cluster_count_x());
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kPairStages; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.tmem_full[i], 1);
+      mbar_init(&s.tmem_empty[i], 2 * kEpilogueWarps);
+    }
+    s.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_x)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything is signalled across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = s.tmem_base;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer (one thread in each CTA)
+    if (lane == 0) {
+      const long long t_start = clock64();
+      const unsigned long long ns_start = global_ns();
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = first_tile; t < total_tiles && ok; t += tile_step) {
+        int mi, ni;
+        pair_tile_coords(tiles_m2, a.tiles_n, t, mi, ni);
+        const int m0 = mi * 2 * kBM + static_cast<int>(rank) * kBM;  // this CTA's 128 rows of the 256-row tile
+        // this CTA's half of the B tile: stacked gating -> leader takes the gate rows, peer the value rows
+        const int nb =
+            GATED == 1 ? (rank == 0 ? ni * 128 : a.n_out + ni * 128) : ni * kBN + static_cast<int>(rank) * 128;
+        for (int kb = 0; kb < a.k_blocks; ++kb) {
+          ok = mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag, a.status, 11);
+          if (!ok) break;
+          if (rank == 0) mbar_expect_tx(&s.full[stage], 2 * kPairStageBytes);  // both CTAs' bytes
+          const uint32_t leader_full = mapa_u32(smem_u32(&s.full[stage]), 0);
+          uint8_t* base = s.stage[stage];
+          tma_load_2d_pair(base, &map_x, leader_full, kb * kBKElems, m0);
+          tma_load_2d_pair(base + kATileBytes, &map_w, leader_full, kb * kBKElems, nb);
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (a.trace != nullptr) {
+        atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 5), static_cast<unsigned long long>(clock64() - t_start));
+        atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 7), global_ns() - ns_start);
+      }
+      if (!ok) {
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1 && rank == 0) {
+    // ---------------------------------------------------------------- MMA issuer (one thread of the leader)
+    if (lane == 0) {
+      const int my_tiles = first_tile < total_tiles ? (total_tiles - 1 - first_tile) / tile_step + 1 : 0;
+      mma_issue_loop<F8, true, kPairStages, kPairStageBytes>(smem_u32(s.stage[0]), s.full, s.empty, s.tmem_full,
+                                                              s.tmem_empty, tmem_base, umma_idesc_pair(ABF), my_tiles,
+                                                              a.k_blocks, abort_flag, a.status, 12, 13);
+    }
+    __syncwarp();
+  } else if (warp >= 2) {
+    // ---------------------------------------------------------------- epilogue (8 warps, both CTAs)
+    const int q = warp & 3;
+    const int colhalf = (warp - 2) >> 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    float alpha = a.alpha_host;
+    if (a.alpha_dev != nullptr) alpha *= __ldg(a.alpha_dev) * __ldg(a.alpha_dev + 1);
+    bool ok = true;
+    for (int t = first_tile; t < total_tiles && ok; t += tile_step) {
+      int mi, ni;
+      pair_tile_coords(tiles_m2, a.tiles_n, t, mi, ni);
+      float* sb = s.bias[warp - 2];
+      stage_bias<GATED, OUT>(a, sb, ni, lane);
+      ok = __all_sync(0xffffffffu, mbar_wait(&s.tmem_full[acc], acc_phase, abort_flag, a.status, 14));
+      if (!ok) break;
+      tc_fence_after();
+      const int row0 = mi * 2 * kBM + static_cast<int>(rank) * kBM + q * 32;
+      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * kBN);
+      epilogue_columns<GATED, ACT, OUT>(a, &map_y, sb, s.out[warp - 2], t_lane, row0, ni, colhalf, alpha, lane);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&s.tmem_empty[acc]), 0));  // the leader counts both CTAs
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (lane == 0) bulk_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees tensor memory or exits while the other may still signal it
+  tc_fence_after();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -422,7 +736,33 @@ static const void* pick_fc1(int act, int gated) {
   }
 }
 
+template <bool F8, int ABF, typename OUT>
+static const void* pick_fc1_pair(int act, int gated) {
+  const bool silu = act == ND_ACT_SILU;
+  switch (gated) {
+    case 1:
+      return silu ? (const void*)fc1_pair_kernel<F8, ABF, 1, ND_ACT_SILU, OUT> : (const void*)fc1_pair_kernel<F8, ABF, 1, ND_ACT_GELU, OUT>;
+    case 2:
+      return silu ? (const void*)fc1_pair_kernel<F8, ABF, 2, ND_ACT_SILU, OUT> : (const void*)fc1_pair_kernel<F8, ABF, 2, ND_ACT_GELU, OUT>;
+    default:
+      return silu ? (const void*)fc1_pair_kernel<F8, ABF, 0, ND_ACT_SILU, OUT> : (const void*)fc1_pair_kernel<F8, ABF, 0, ND_ACT_GELU, OUT>;
+  }
+}
+
+static std::atomic<int> g_fc1_pair{-1};  // -1 = choose per problem
+static std::atomic<long long*> g_fc1_trace{nullptr};
+
 }  // namespace nd
+
+// Tuning hook: 1 = two-CTA tiles (cta_group::2, clusters of two CTAs), 0 = single-CTA tiles, negative (the
+// default) = choose per problem. Process-wide.
+extern "C" void nd_tune_fc1_pair(int mode) { nd::g_fc1_pair.store(mode < 0 ? -1 : (mode != 0 ? 1 : 0)); }
+
+// Diagnostic hook: when set to a device array of 8 int64, later launches add to it, summed over CTAs: [0] cycles
+// the copy-issuing thread waited for free stages, [3] cycles one epilogue warp waited for an accumulator, [4]
+// cycles that warp spent on tiles, [5] the copy-issuing thread's lifetime in cycles and [7] in nanoseconds (their
+// ratio is the SM clock during the launch). The two-CTA kernel reports [5] and [7] only. nullptr turns it off.
+extern "C" void nd_tune_fc1_trace(long long* device_counters) { nd::g_fc1_trace.store(device_counters); }
 
 extern "C" int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const void* x, const void* w,
                           const void* bias, float alpha_host, const float* alpha_dev, void* y, int64_t m,
@@ -444,6 +784,7 @@ extern "C" int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const
 
   Fc1Args a{};
   a.bias = bias; a.y = y; a.alpha_dev = alpha_dev; a.status = status; a.alpha_host = alpha_host;
+  a.trace = g_fc1_trace.load(std::memory_order_relaxed);
   a.m = static_cast<int>(m); a.k = static_cast<int>(k); a.n = static_cast<int>(n);
   a.n_out = static_cast<int>(n_out);
   a.tiles_m = static_cast<int>((m + kBM - 1) / kBM);
@@ -458,26 +799,80 @@ extern "C" int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const
                                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   if (!make_map(&map_x, dt, es, x, m, k) || !make_map(&map_w, dt, es, w, n, k)) return ND_ERR_LAUNCH;
 
-  const void* fn;
-  const int g = gated;
-  if (ab_dtype == ND_E4M3)
-    fn = out_dtype == ND_BF16 ? pick_fc1<true, 0, __nv_bfloat16>(act, g) : pick_fc1<true, 0, __half>(act, g);
-  else if (ab_dtype == ND_BF16)
-    fn = out_dtype == ND_BF16 ? pick_fc1<false, 1, __nv_bfloat16>(act, g) : pick_fc1<false, 1, __half>(act, g);
-  else
-    fn = out_dtype == ND_BF16 ? pick_fc1<false, 0, __nv_bfloat16>(act, g) : pick_fc1<false, 0, __half>(act, g);
+  // y as a tensor for the epilogue's block stores: n_out contiguous 16-bit columns, blocks of 32 x 32, 64B swizzle
+  CUtensorMap map_y;
+  {
+    EncodeTiledFn enc = encode_fn();
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(n_out), static_cast<cuuint64_t>(m)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(n_out) * 2};
+    const cuuint32_t box[2] = {32u, 32u};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUtensorMapDataType ydt = out_dtype == ND_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (enc == nullptr ||
+        enc(&map_y, ydt, 2, y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return ND_ERR_LAUNCH;
+  }
 
-  const int smem_bytes = static_cast<int>(sizeof(Fc1Smem)) + 1024;
+  const int g = gated;
+  // Two-CTA tiles halve the B-operand bytes each SM stages and keep the tensor pipe busier per k-block, but the
+  // pair's epilogues run in lockstep and a 256-row tile wastes more on small problems: measured faster for
+  // 16-bit operands once there are at least two rounds of single-CTA tiles, slower for FP8 (half the k-blocks
+  // per tile, so the epilogue weighs twice as much).
+  const int pair_mode = g_fc1_pair.load(std::memory_order_relaxed);
+  const bool pair = pair_mode >= 0 ? pair_mode != 0 : (ab_dtype != ND_E4M3 && tiles >= 2LL * sm_count());
+  const void* fn;
+  if (pair) {
+    if (ab_dtype == ND_E4M3)
+      fn = out_dtype == ND_BF16 ? pick_fc1_pair<true, 0, __nv_bfloat16>(act, g) : pick_fc1_pair<true, 0, __half>(act, g);
+    else if (ab_dtype == ND_BF16)
+      fn = out_dtype == ND_BF16 ? pick_fc1_pair<false, 1, __nv_bfloat16>(act, g) : pick_fc1_pair<false, 1, __half>(act, g);
+    else
+      fn = out_dtype == ND_BF16 ? pick_fc1_pair<false, 0, __nv_bfloat16>(act, g) : pick_fc1_pair<false, 0, __half>(act, g);
+  } else {
+    if (ab_dtype == ND_E4M3)
+      fn = out_dtype == ND_BF16 ? pick_fc1<true, 0, __nv_bfloat16>(act, g) : pick_fc1<true, 0, __half>(act, g);
+    else if (ab_dtype == ND_BF16)
+      fn = out_dtype == ND_BF16 ? pick_fc1<false, 1, __nv_bfloat16>(act, g) : pick_fc1<false, 1, __half>(act, g);
+    else
+      fn = out_dtype == ND_BF16 ? pick_fc1<false, 0, __nv_bfloat16>(act, g) : pick_fc1<false, 0, __half>(act, g);
+  }
+
+  const int smem_bytes = static_cast<int>(pair ? sizeof(Fc1PairSmem) : sizeof(Fc1Smem)) + 1024;
   cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) {
     set_last_cuda_error(e);
     (void)cudaGetLastError();
     return ND_ERR_LAUNCH;
   }
-  const long long grid = tiles < sm_count() ? tiles : sm_count();
-  void* params[] = {&map_x, &map_w, &a};
-  e = cudaLaunchKernel(fn, dim3(static_cast<unsigned>(grid)), dim3(kThreads), params, smem_bytes,
-                       static_cast<cudaStream_t>(stream));
+  void* params[] = {&map_x, &map_w, &map_y, &a};
+  cudaLaunchConfig_t cfg{};
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr{};
+  if (pair) {
+    // persistent grid of CTA pairs: as many clusters of two as can be resident, at most one per tile
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const long long pair_tiles = static_cast<long long>((a.m + 2 * kBM - 1) / (2 * kBM)) * a.tiles_n;
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * (sm_count() / 2)));
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, fn, &cfg) != cudaSuccess || clusters < 1) {
+      (void)cudaGetLastError();
+      clusters = sm_count() / 2;
+    }
+    if (clusters > pair_tiles) clusters = static_cast<int>(pair_tiles);
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+  } else {
+    const long long grid = tiles < sm_count() ? tiles : sm_count();
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  }
+  e = cudaLaunchKernelExC(&cfg, fn, params);
   if (e != cudaSuccess) {
     set_last_cuda_error(e);
     (void)cudaGetLastError();

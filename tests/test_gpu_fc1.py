@@ -62,6 +62,53 @@ def test_matches_oracle(act, layout, dtype, mkn, bias):
     assert_half_parity(y, exact.to(dtype), f"fc1 {act} layout {layout} {dtype} {mkn}", exact=exact)
 
 
+@pytest.fixture
+def tile_mode():
+    """Forces single-CTA (0) or two-CTA (1) tiles for one test and restores the per-problem choice."""
+    lib = capi.lib()
+
+    def force(mode):
+        lib.nd_tune_fc1_pair(mode)
+
+    yield force
+    lib.nd_tune_fc1_pair(-1)
+
+
+@pytest.mark.parametrize("pair", [0, 1])
+@pytest.mark.parametrize("layout", [0, 1, 2])
+@pytest.mark.parametrize("dtype,mkn", [
+    (torch.bfloat16, (300, 200, 272)),     # ragged in M (also against the 256-row pair tile), K and N
+    (torch.float16, (129, 1152, 528)),     # one row into the second CTA of a pair
+    (torch.bfloat16, (1, 64, 16)),
+    (torch.bfloat16, (1024, 1152, 4608)),  # more tiles than CTAs: every CTA walks several tiles and ring wraps
+])
+def test_both_tile_modes_match_oracle(tile_mode, pair, layout, dtype, mkn):
+    m, k, n = mkn
+    tile_mode(pair)
+    x, w, b = synth.fc1_inputs(m, k, n, dtype, seed=77 + m % 5)
+    y = run(x, w, b, "gelu", layout)
+    exact = oracle.fc1_fwd(x, w, b, "gelu", gated=layout != 0, compute=torch.float64, out_dtype=torch.float64)
+    assert_half_parity(y, exact.to(dtype), f"fc1 pair={pair} layout {layout} {dtype} {mkn}", exact=exact)
+
+
+@pytest.mark.parametrize("pair", [0, 1])
+def test_both_tile_modes_fp8(tile_mode, pair):
+    m, k, n = 512, 1152, 4608
+    tile_mode(pair)
+    x, w, b = synth.fc1_inputs(m, k, n, torch.bfloat16, seed=5)
+    qx, sx = capi.quantize_e4m3(x.to(DEV))
+    qw, sw = capi.quantize_e4m3(w.to(DEV))
+    status = new_status()
+    y = capi.fc1_fwd(qx, qw, b.to(DEV), "silu", 1, alpha_dev=torch.cat([sx, sw]), out_dtype=torch.bfloat16,
+                     status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    oqx, osx = oracle.quant_e4m3(x)
+    oqw, osw = oracle.quant_e4m3(w)
+    want = oracle.fc1_fwd_fp8(oqx, osx, oqw, osw, b, "silu", gated=True)
+    assert oracle.rel_l2(y.cpu(), want) < FP8_REL_L2
+
+
 @pytest.mark.parametrize("layout", [0, 1])
 def test_config4_bf16(layout):
     """Workload config 4: M=8192, K=1152, N=4608, bias, GELU-tanh, bf16 (gated as in the reference, and plain)."""
