@@ -114,17 +114,21 @@ def _need_cuda(*ts: torch.Tensor) -> None:
 
 
 class Workspace:
-    """A cached, 256-byte aligned device scratch buffer (grown on demand, never initialised)."""
+    """Cached, 256-byte aligned device scratch buffers (grown on demand, never initialised), one per device
+    and stream: launches on different streams may run concurrently and must not share scratch."""
 
     def __init__(self) -> None:
-        self.buf: torch.Tensor | None = None
+        self.bufs: dict[tuple, torch.Tensor] = {}
 
-    def get(self, nbytes: int, device) -> torch.Tensor | None:
+    def get(self, nbytes: int, device, stream: int = 0) -> torch.Tensor | None:
         if nbytes == 0:
             return None
-        if self.buf is None or self.buf.numel() < nbytes or self.buf.device != torch.device(device):
-            self.buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        return self.buf
+        key = (torch.device(device), stream)
+        buf = self.bufs.get(key)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            self.bufs[key] = buf
+        return buf
 
 
 _WS = Workspace()
@@ -185,8 +189,9 @@ def norm_bwd(kind, dy, x, scale, mean, invstd, *, mode="fused", row_start=0, seq
         if dshift is None:
             dshift = torch.zeros(batch, hidden, dtype=torch.float32, device=x.device)
         ws_bytes = L.nd_norm_dparam_ws_bytes(rows, row_start, seq_len, hidden)
-        ws_t = (ws or _WS).get(ws_bytes, x.device)
     st = _stream()
+    if want_dp:
+        ws_t = (ws or _WS).get(ws_bytes, x.device, st or 0)
     shape = (rows, row_start, seq_len, hidden)
     if kind == "layer":
         if mode == "dx":

@@ -161,6 +161,74 @@ def test_row_tile_height_does_not_change_results_beyond_rounding(tile_rows):
     compare_all("layer", got, want, f"tile_rows {tile_rows}")
 
 
+class _DirtyWorkspace(capi.Workspace):
+    """Scratch that starts out full of ones in every bit: the library must not rely on its contents."""
+
+    def get(self, nbytes, device, stream=0):
+        fresh = (torch.device(device), stream) not in self.bufs
+        buf = super().get(nbytes, device, stream)
+        if fresh and buf is not None:
+            buf.fill_(0xFF)
+        return buf
+
+
+@pytest.mark.parametrize("kind", ["layer", "rms"])
+@pytest.mark.parametrize("mode", ["fused", "dparam"])
+@pytest.mark.parametrize("shape,row_lo,row_hi", [
+    ((32, 256, 1152), 0, None),      # the benchmark shape: one or two samples per chunk of rows
+    ((6, 300, 768), 0, None),
+    ((5, 640, 1152), 700, 2900),     # a shard that starts and ends inside samples
+    ((2, 4096, 128), 0, None),       # long samples: many partial slots per sample
+])
+def test_dparam_does_not_depend_on_scratch_contents_or_replay(kind, mode, shape, row_lo, row_hi):
+    """dscale/dshift are bit-identical from scratch memory that was never cleared, launch after launch on the
+    same scratch, and under CUDA-graph replay."""
+    b, s_len, h = shape
+    x, scale, shift, dy = synth.norm_inputs(b, s_len, h, torch.bfloat16, 31)
+    xd, sd, hd, gd = (t.to(DEV) for t in (x, scale, shift, dy))
+    if kind == "layer":
+        _, mean, invstd = capi.norm_fwd(kind, xd, sd, hd, 1e-6)
+    else:
+        _, invstd = capi.norm_fwd(kind, xd, sd, hd, 1e-6)
+        mean = None
+    row_hi = b * s_len if row_hi is None else row_hi
+    rows = slice(row_lo, row_hi)
+    xs, gs = xd.reshape(-1, h)[rows].contiguous(), gd.reshape(-1, h)[rows].contiguous()
+    ms = None if mean is None else mean.reshape(-1)[rows].contiguous()
+    vs = invstd.reshape(-1)[rows].contiguous()
+
+    def bwd(ws, **kw):
+        return capi.norm_bwd(kind, gs, xs, sd, ms, vs, mode=mode, row_start=row_lo, seq_len=s_len, batch=b, ws=ws, **kw)
+
+    _, want_ds, want_dh = bwd(capi.Workspace())
+    torch.cuda.synchronize()
+    ws = _DirtyWorkspace()
+    for attempt in range(3):
+        _, ds, dh = bwd(ws)
+        torch.cuda.synchronize()
+        assert torch.equal(ds, want_ds) and torch.equal(dh, want_dh), f"launch {attempt} on the same scratch"
+    ds, dh = torch.zeros_like(want_ds), torch.zeros_like(want_dh)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        bwd(ws, dscale=ds, dshift=dh)  # sizes this stream's scratch before the capture
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            bwd(ws, dscale=ds, dshift=dh)
+    for replay in range(3):
+        ds.fill_(7.0)
+        dh.fill_(7.0)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        touched = ds.ne(7.0).any(dim=1)  # samples of the shard
+        assert touched.any()
+        assert torch.equal(ds[touched], want_ds[touched]) and torch.equal(dh[touched], want_dh[touched]), \
+            f"graph replay {replay}"
+    assert capi.lib().nd_device_error(0) == 0
+
+
 def test_dparam_is_deterministic_run_to_run():
     x, scale, shift, dy = synth.norm_inputs(8, 256, 1152, torch.bfloat16, 6)
     first = run_fwd_bwd("layer", x, scale, shift, dy, 1e-6)
