@@ -189,6 +189,10 @@ int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const void* x, c
                const void* bias, float alpha_host, const float* alpha_dev, void* y, int64_t m,
                int64_t k, int64_t n, int* status, void* stream);
 
+/* Tuning hook for the gate-act kernels: rows per CTA group (1, 2 or 4; 0 = default) and 1 = a single
+ * resident wave of CTAs striding over the groups instead of one CTA per group (default 0). Process-wide.
+ * No counterpart in the reference. */
+void nd_tune_gate_act(int rows_per_group, int persistent);
 /* Tuning hook: 1 = two-CTA tiles (tcgen05 cta_group::2 over clusters of two CTAs), 0 = single-CTA
  * tiles, negative (default) = chosen per problem. Process-wide. No counterpart in the reference. */
 void nd_tune_fc1_pair(int mode);

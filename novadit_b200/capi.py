@@ -59,6 +59,7 @@ SIGNATURES = {
                                 c_void_p]),
     "nd_fc1_fwd": (c_int, [c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float,
                            c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "nd_tune_gate_act": (None, [c_int, c_int]),
     "nd_tune_fc1_pair": (None, [c_int]),
     "nd_tune_fc1_trace": (None, [c_void_p]),
     "nd_amax_ws_bytes": (c_size_t, []),
