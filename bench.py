@@ -416,7 +416,7 @@ def run_gpu_arm(args) -> None:
                          "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": NCU_TRAFFIC_BWD, "peak_source": peak_src, "algorithmic_bytes": BWD_BYTES,
                          "avg_launch_ms": bwd_ms},
-            "e2e": e2e_line, "gpu_launches": 2 * steps, "clocks": clocks,
+            "e2e": e2e_line, "gpu_launches": 3 * steps, "clocks": clocks,
             "cpu_baseline": cpu_line, "extras": extras,
         }
         print(json.dumps(line), flush=True)
