@@ -172,8 +172,9 @@ extern "C" {
 // norm kernels (0 restores the built-in choice). Process-wide.
 void nd_tune_norm_tile_rows(int tile_rows) { g_tile_rows_override.store(tile_rows < 0 ? 0 : tile_rows); }
 
-// Tuning hook: which instantiation of the hot norm kernels to launch (rows in flight per thread,
-// prefetch on/off, register cap); 0 = default. Process-wide.
+// Tuning hook: 0 = default; 1 = the generic (register-fed) kernels even where the bulk-copy kernels apply;
+// 3 / 4 = never / always use the warp-per-row forward kernel where it applies (default: large tensors only).
+// Process-wide.
 void nd_tune_norm_variant(int variant) { g_norm_variant.store(variant); }
 // Tuning hook: shared-memory pipeline depth of the bulk-copy norm kernels (0 = as many as fit).
 void nd_tune_norm_stages(int stages) { g_norm_stages.store(stages < 0 ? 0 : stages); }

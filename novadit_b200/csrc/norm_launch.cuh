@@ -1,13 +1,15 @@
 // Host-side selection and launch of the AdaLN / AdaRMSNorm kernels.
 //
 // Rows that are 16-byte vectorisable and at most 512 vectors wide (H <= 4096 for 16-bit types)
-// take the bulk-copy kernels of norm_tma.cuh: one balanced wave of CTAs, one chunk of rows each.
+// take the bulk-copy kernels: one balanced wave of CTAs, one chunk of rows each, one CTA per row group
+// (norm_tma.cuh); the forward pass of large tensors with rows up to 192 vectors wide runs one warp per row
+// (norm_warp.cuh).
 // Everything else (ragged or misaligned rows, very wide rows) takes the generic kernels of
 // norm_impl.cuh, which cut the rows into (sample, tile) items. A backward launch that produces
 // dscale/dshift is followed by the small stage-2 kernel that sums the fp32 partials.
 #pragma once
 
-#include "norm_tma.cuh"
+#include "norm_warp.cuh"
 
 namespace nd {
 
@@ -54,8 +56,57 @@ inline long long resident_slots(const void* fn, int nt, int smem, bool fwd = tru
   return static_cast<long long>(occ) * sm_count();
 }
 
+template <typename T, int VEC, int NV>
+static const void* pick_fwd_warp_nv(bool rms) {
+  return rms ? (const void*)norm_fwd_warp<T, VEC, NV, true> : (const void*)norm_fwd_warp<T, VEC, NV, false>;
+}
+
+// the warp-per-row forward kernel for rows of up to 6 x 32 vectors (H <= 1536 for 16-bit types); null beyond
+template <typename T, int VEC>
+static const void* pick_fwd_warp(int nvec, bool rms) {
+  switch ((nvec + 31) / 32) {
+    case 1: return pick_fwd_warp_nv<T, VEC, 1>(rms);
+    case 2: return pick_fwd_warp_nv<T, VEC, 2>(rms);
+    case 3: return pick_fwd_warp_nv<T, VEC, 3>(rms);
+    case 4: return pick_fwd_warp_nv<T, VEC, 4>(rms);
+    case 5: return pick_fwd_warp_nv<T, VEC, 5>(rms);
+    case 6: return pick_fwd_warp_nv<T, VEC, 6>(rms);
+    default: return nullptr;
+  }
+}
+
+// Forward with one warp per row (norm_warp.cuh): 128-thread CTAs, one chunk of rows each, a single wave.
+template <typename T, int VEC>
+int launch_norm_fwd_warp(NormArgs a, const void* fn, cudaStream_t st) {
+  int stages = norm_stages_override() > 0 ? norm_stages_override() : 2;
+  if (stages < 2) stages = 2;
+  if (stages > kMaxStages) stages = kMaxStages;
+  a.stages = stages;
+  const int smem = static_cast<int>(norm_warp_smem(a.hidden, static_cast<int>(sizeof(T)), stages));
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    (void)cudaGetLastError();
+    return ND_ERR_LAUNCH;
+  }
+  long long chunks = resident_slots(fn, kWarpThreads, smem, true);
+  const long long most = a.rows / kWarpRows > 1 ? a.rows / kWarpRows : 1;  // every chunk holds at least one full group
+  if (chunks > most) chunks = most;
+  a.n_chunks = static_cast<int>(chunks);
+  a.chunk_base = a.rows / chunks;
+  a.chunk_rem = static_cast<int>(a.rows % chunks);
+  a.b_first = a.row_start / a.seq_len;
+  a.n_samples = (a.row_start + a.rows - 1) / a.seq_len - a.b_first + 1;
+  return launch_checked(fn, chunks, kWarpThreads, a, smem, st);
+}
+
 template <typename T, int VEC>
 int launch_norm_tma(NormArgs a, cudaStream_t st) {
+  // forward of a large tensor (128 MB and up): one warp per row; measured faster there and slower below
+  const bool large = static_cast<double>(a.rows) * a.hidden * sizeof(T) >= 128.0 * 1024 * 1024;
+  if (a.mode == kFwd && (norm_variant() == 4 || (large && norm_variant() != 3))) {
+    if (const void* fw = pick_fwd_warp<T, VEC>(a.hidden / VEC, a.rms)) return launch_norm_fwd_warp<T, VEC>(a, fw, st);
+  }
   constexpr int RPI = 4;
   const int nvec = a.hidden / VEC;
   const int nt = (nvec + 31) / 32 * 32;

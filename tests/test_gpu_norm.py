@@ -126,7 +126,7 @@ def test_inference_equals_training_output_bitwise(kind):
 
 
 @pytest.mark.parametrize("kind", ["layer", "rms"])
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 3, 4])
 def test_every_kernel_variant_meets_the_bars(kind, variant):
     """The tuning knob selects among instantiations of the hot kernels; each must be correct."""
     x, scale, shift, dy = synth.norm_inputs(5, 77, 1152, torch.bfloat16, 8)
@@ -146,6 +146,47 @@ def test_every_kernel_variant_meets_the_bars(kind, variant):
         assert L.nd_device_error(0) == 0, "a bounded device-side wait expired"
     finally:
         L.nd_tune_norm_variant(0)
+
+
+@pytest.mark.parametrize("kind", ["layer", "rms"])
+@pytest.mark.parametrize("dtype,shape", [
+    (torch.bfloat16, (3, 77, 1152)),    # 4.5 passes per lane, ragged groups at every sample end
+    (torch.float16, (2, 130, 768)),     # 3 full passes
+    (torch.bfloat16, (5, 9, 128)),      # half a pass, samples shorter than three groups
+    (torch.bfloat16, (2, 40, 1536)),    # 6 passes, the widest row of this kernel
+    (torch.bfloat16, (1, 1, 64)),       # a single row
+    (torch.float32, (2, 33, 768)),      # fp32 rows: 4 elements per vector, 6 passes
+])
+def test_warp_per_row_forward_kernel(kind, dtype, shape):
+    """The forward kernel the launcher picks for large tensors, forced on small ones: full result, statistics
+    off (inference), and a shard that starts and ends inside samples."""
+    b, s_len, h = shape
+    x, scale, shift, dy = synth.norm_inputs(b, s_len, h, dtype, 17)
+    want = oracle_fwd_bwd(kind, x, scale, shift, dy, 1e-6)
+    xd, sd, hd = x.to(DEV), scale.to(DEV), shift.to(DEV)
+    L = capi.lib()
+    try:
+        L.nd_tune_norm_variant(4)
+        out = capi.norm_fwd(kind, xd, sd, hd, 1e-6)
+        y_inf = capi.norm_fwd(kind, xd, sd, hd, 1e-6, stats=False)[0]
+        rows = b * s_len
+        lo, hi = rows // 3, rows - rows // 4
+        part = capi.norm_fwd(kind, xd.reshape(-1, h)[lo:hi].contiguous(), sd, hd, 1e-6, row_start=lo, seq_len=s_len)
+        torch.cuda.synchronize()
+    finally:
+        L.nd_tune_norm_variant(0)
+    y, stats = out[0], out[1:]
+    if dtype == torch.float32:
+        assert_parity(y, want[0], "y")
+    else:
+        assert_half_parity(y, want[0], "y", exact=want[6])
+    if kind == "layer":
+        assert_f32_parity(stats[0].reshape(want[1].shape), want[1], "mean", tol=1e-4)
+    assert_f32_parity(stats[-1].reshape(want[2].shape), want[2], "invstd", tol=1e-5)
+    assert torch.equal(y_inf, y)
+    assert torch.equal(part[0], y.reshape(-1, h)[lo:hi])
+    assert torch.equal(part[-1].reshape(-1), stats[-1].reshape(-1)[lo:hi])
+    assert L.nd_device_error(0) == 0
 
 
 @pytest.mark.parametrize("tile_rows", [1, 8, 24, 64, 1000])
