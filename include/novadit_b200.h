@@ -170,6 +170,31 @@ int nd_gate_act_fwd(int dtype, int act, const void* x, void* y, int64_t rows, in
 int nd_gate_act_bwd(int dtype, int act, const void* dy, const void* x, void* dz, int64_t rows,
                     int64_t inter, void* stream);
 
+/* The same backward for rows laid out [gate(I) | up(I)]: FC1's pre-activation z = x W^T + b with the
+ * nn.Linear weight as stored (gate block first), dz = [dy * up * act'(gate) | dy * act(gate)]. Replaces
+ * the eager PyTorch activation backward of the reference's FC1 autograd Function,
+ * novadit/ops/fc1_bias_act.py:255-270. */
+int nd_gate_act_bwd_gate_first(int dtype, int act, const void* dy, const void* z, void* dz,
+                               int64_t rows, int64_t inter, void* stream);
+
+/* --------------------------------------------------------------- row operators next to the path */
+
+/* y = x + residual (+ bias[h]) over [rows, hidden]; fp32 sum, one rounding. dtype ND_F16 / ND_BF16 /
+ * ND_F32; bias may be NULL. The reference specifies this operator (novadit/ops/residual.py:8-25,
+ * binding fused_out_residual_forward csrc/bindings.cpp:93) but its kernel is a stub that raises
+ * (csrc/ops/residual_kernel.cu:3-8). */
+int nd_out_residual_fwd(int dtype, const void* x, const void* residual, const void* bias, void* y,
+                        int64_t rows, int64_t hidden, void* stream);
+
+/* Rows of qkv [rows, 3*hidden] split into q, k, v [rows, hidden] (hidden = heads * head_dim, so the
+ * outputs are the contiguous [B, S, heads, head_dim] tensors of novadit/ops/qkv_pack.py:9-23), and the
+ * inverse for the backward pass. Binding fused_qkv_pack_forward csrc/bindings.cpp:91; the reference's
+ * kernel is a stub that raises (csrc/ops/qkv_pack_kernel.cu:5-10). */
+int nd_qkv_pack_fwd(int dtype, const void* qkv, void* q, void* k, void* v, int64_t rows,
+                    int64_t hidden, void* stream);
+int nd_qkv_pack_bwd(int dtype, const void* dq, const void* dk, const void* dv, void* dqkv,
+                    int64_t rows, int64_t hidden, void* stream);
+
 /* -------------------------------------------------------------------- FC1 */
 
 /* z = (x @ w^T) * alpha + bias, x [m,k] and w [n,k] both K-contiguous (nn.Linear layout).

@@ -40,6 +40,7 @@ CU_SOURCES = [
     "norm_bf16.cu",
     "norm_f32.cu",
     "gate_act.cu",
+    "rowops.cu",
     "quant.cu",
     "fc1.cu",
     "noalloc.cu",

@@ -57,6 +57,11 @@ SIGNATURES = {
     "nd_gate_act_fwd": (c_int, [c_int, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "nd_gate_act_bwd": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                 c_void_p]),
+    "nd_gate_act_bwd_gate_first": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                           c_void_p]),
+    "nd_out_residual_fwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "nd_qkv_pack_fwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "nd_qkv_pack_bwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "nd_fc1_fwd": (c_int, [c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float,
                            c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "nd_tune_gate_act": (None, [c_int, c_int]),
@@ -228,13 +233,15 @@ def gate_act_fwd(x, act="silu", y=None):
     return y
 
 
-def gate_act_bwd(dy, x, act="silu", dz=None):
+def gate_act_bwd(dy, x, act="silu", dz=None, gate_first=False):
+    """dz for rows [up | gate] (default) or [gate | up] (`gate_first`: FC1's pre-activation layout)."""
     _need_cuda(dy, x)
     inter = x.shape[-1] // 2
     rows = x.numel() // (2 * inter)
     dz = torch.empty_like(x) if dz is None else dz
-    check(lib().nd_gate_act_bwd(DTYPE_IDS[x.dtype], ACT_IDS[act], _ptr(dy), _ptr(x), _ptr(dz), rows, inter,
-                                _stream()), "nd_gate_act_bwd")
+    fn = lib().nd_gate_act_bwd_gate_first if gate_first else lib().nd_gate_act_bwd
+    check(fn(DTYPE_IDS[x.dtype], ACT_IDS[act], _ptr(dy), _ptr(x), _ptr(dz), rows, inter, _stream()),
+          "nd_gate_act_bwd_gate_first" if gate_first else "nd_gate_act_bwd")
     return dz
 
 

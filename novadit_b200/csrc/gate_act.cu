@@ -16,6 +16,7 @@ struct GateArgs {
   void* out;       // y [rows, I] or dz [rows, 2I]
   long long rows;
   int inter;
+  int gate_first;  // 0: rows are [up | gate] (the gate-act operator); 1: rows are [gate | up] (FC1's z = x W^T + b)
 };
 
 // PASSES > 0: the row needs exactly that many passes of the CTA's threads and all of them are unrolled, so
@@ -30,6 +31,7 @@ __global__ void __launch_bounds__(256) gate_act_kernel(const GateArgs a) {
   const long long groups = (a.rows + RG - 1) / RG;
   const long long in_stride = 2LL * I;
   const long long out_stride = BWD ? 2LL * I : I;
+  const int up_off = a.gate_first ? I : 0, gate_off = a.gate_first ? 0 : I;  // halves of an input / dz row
   constexpr int NP = PASSES > 0 ? PASSES : 1;
 
   for (long long g = blockIdx.x; g < groups; g += gridDim.x) {
@@ -47,8 +49,8 @@ __global__ void __launch_bounds__(256) gate_act_kernel(const GateArgs a) {
           if constexpr (BWD) gy[p][j].zero();
           if (iv < nvec && r0 + j < a.rows) {
             const T* row = x + (r0 + j) * in_stride;
-            up[p][j].load_stream(row + col);
-            gate[p][j].load_stream(row + I + col);
+            up[p][j].load_stream(row + up_off + col);
+            gate[p][j].load_stream(row + gate_off + col);
             if constexpr (BWD) gy[p][j].load_stream(dy + (r0 + j) * I + col);
           }
         }
@@ -84,8 +86,8 @@ __global__ void __launch_bounds__(256) gate_act_kernel(const GateArgs a) {
               o0.pack(du);
               o1.pack(dg);
               T* orow = out + (r0 + j) * out_stride;
-              o0.store(orow + col);
-              o1.store(orow + I + col);
+              o0.store(orow + up_off + col);
+              o1.store(orow + gate_off + col);
             }
           }
         }
@@ -175,13 +177,13 @@ static int launch_gate(GateArgs a, int act, bool bwd, cudaStream_t st) {
 }
 
 static int gate_entry(int dtype, int act, bool bwd, const void* dy, const void* x, void* out,
-                      int64_t rows, int64_t inter, void* stream) {
+                      int64_t rows, int64_t inter, void* stream, int gate_first = 0) {
   if (rows < 0 || inter <= 0) return ND_ERR_BAD_ARG;
   if (act != ND_ACT_SILU && act != ND_ACT_GELU) return ND_ERR_UNSUPPORTED;
   if (inter > INT32_MAX / 2) return ND_ERR_UNSUPPORTED;
   if (rows == 0) return ND_OK;
   if (!x || !out || (bwd && !dy)) return ND_ERR_BAD_ARG;
-  GateArgs a{x, dy, out, rows, static_cast<int>(inter)};
+  GateArgs a{x, dy, out, rows, static_cast<int>(inter), gate_first != 0 ? 1 : 0};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case ND_F16: return launch_gate<__half>(a, act, bwd, st);
@@ -210,6 +212,13 @@ int nd_gate_act_fwd(int dtype, int act, const void* x, void* y, int64_t rows, in
 int nd_gate_act_bwd(int dtype, int act, const void* dy, const void* x, void* dz, int64_t rows,
                     int64_t inter, void* stream) {
   return nd::gate_entry(dtype, act, true, dy, x, dz, rows, inter, stream);
+}
+
+// The same backward for rows laid out [gate(I) | up(I)], which is FC1's pre-activation z = x W^T + b with the
+// nn.Linear weight as stored: dz = [dy * up * act'(gate) | dy * act(gate)].
+int nd_gate_act_bwd_gate_first(int dtype, int act, const void* dy, const void* z, void* dz, int64_t rows,
+                               int64_t inter, void* stream) {
+  return nd::gate_entry(dtype, act, true, dy, z, dz, rows, inter, stream, 1);
 }
 
 }  // extern "C"

@@ -1,0 +1,169 @@
+// The two row operators the reference specifies but never implemented (sm_100a):
+//   out-residual  y = x + residual (+ bias[h])            novadit/ops/residual.py:8-25, stub csrc/ops/residual_kernel.cu
+//   QKV pack      [rows, 3H] -> q, k, v [rows, H] (+ back) novadit/ops/qkv_pack.py:9-44, stub csrc/ops/qkv_pack_kernel.cu
+// Pure streaming work, laid out like the gate-act kernels: one CTA per row, thread t handles 16-byte vectors
+// t, t + NT, ... of the row, fp32 math for the sum, one rounding on store. Misaligned or odd-width rows take
+// the same kernels with one element per "vector".
+#include "common.cuh"
+
+namespace nd {
+
+struct ResidualArgs {
+  const void* x;
+  const void* residual;
+  const void* bias;  // [hidden] or null
+  void* y;
+  long long rows;
+  int hidden;
+};
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) out_residual_kernel(const ResidualArgs a) {
+  const int nvec = a.hidden / VEC;
+  const T* __restrict__ bias = static_cast<const T*>(a.bias);
+  for (long long row = blockIdx.x; row < a.rows; row += gridDim.x) {
+    const T* __restrict__ x = static_cast<const T*>(a.x) + row * a.hidden;
+    const T* __restrict__ r = static_cast<const T*>(a.residual) + row * a.hidden;
+    T* __restrict__ y = static_cast<T*>(a.y) + row * a.hidden;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      Vec<T, VEC> vx, vr, vb;
+      vx.load_stream(x + v * VEC);
+      vr.load_stream(r + v * VEC);
+      float fx[VEC], fr[VEC], fb[VEC];
+      vx.unpack(fx);
+      vr.unpack(fr);
+      if (bias != nullptr) {
+        vb.load(bias + v * VEC);
+        vb.unpack(fb);
+      } else {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) fb[k] = 0.f;
+      }
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) fx[k] = (fx[k] + fr[k]) + fb[k];
+      Vec<T, VEC> o;
+      o.pack(fx);
+      o.store(y + v * VEC);
+    }
+  }
+}
+
+struct QkvArgs {
+  void* qkv;      // [rows, 3H]
+  void* part[3];  // q, k, v: [rows, H] each
+  long long rows;
+  int hidden;
+};
+
+// PACK: qkv -> q, k, v; otherwise q, k, v -> qkv (the backward of the pack)
+template <typename T, int VEC, bool PACK>
+__global__ void __launch_bounds__(256) qkv_pack_kernel(const QkvArgs a) {
+  const int nvec = a.hidden / VEC;
+  for (long long row = blockIdx.x; row < a.rows; row += gridDim.x) {
+    T* wide = static_cast<T*>(a.qkv) + row * 3LL * a.hidden;
+#pragma unroll
+    for (int p = 0; p < 3; ++p) {
+      T* narrow = static_cast<T*>(a.part[p]) + row * a.hidden;
+      T* w = wide + static_cast<long long>(p) * a.hidden;
+      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        Vec<T, VEC> t;
+        if (PACK) {
+          t.load_stream(w + v * VEC);
+          t.store(narrow + v * VEC);
+        } else {
+          t.load_stream(narrow + v * VEC);
+          t.store(w + v * VEC);
+        }
+      }
+    }
+  }
+}
+
+static int threads_for(int nvec) {
+  const int passes = (nvec + 255) / 256;
+  int nt = ((nvec + passes - 1) / passes + 31) / 32 * 32;
+  return nt < 32 ? 32 : nt;
+}
+
+static int launch(const void* fn, void* args, long long rows, int nt, cudaStream_t st) {
+  long long grid = rows < 0x7FFFFFFFLL ? rows : 0x7FFFFFFFLL;  // the kernels stride over rows
+  if (grid < 1) return ND_OK;
+  void* params[] = {args};
+  cudaError_t e = cudaLaunchKernel(fn, dim3(static_cast<unsigned>(grid)), dim3(nt), params, 0, st);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    (void)cudaGetLastError();
+    return ND_ERR_LAUNCH;
+  }
+  return ND_OK;
+}
+
+template <typename T>
+static int launch_residual(ResidualArgs a, cudaStream_t st) {
+  constexpr int VMAX = 16 / sizeof(T);
+  const bool vec_ok = a.hidden % VMAX == 0 && aligned16(a.x) && aligned16(a.residual) && aligned16(a.y) &&
+                      aligned16(a.bias);
+  if (vec_ok) return launch(reinterpret_cast<const void*>(out_residual_kernel<T, VMAX>), &a, a.rows, threads_for(a.hidden / VMAX), st);
+  return launch(reinterpret_cast<const void*>(out_residual_kernel<T, 1>), &a, a.rows, threads_for(a.hidden), st);
+}
+
+template <typename T>
+static int launch_qkv(QkvArgs a, bool pack, cudaStream_t st) {
+  constexpr int VMAX = 16 / sizeof(T);
+  const bool vec_ok = a.hidden % VMAX == 0 && aligned16(a.qkv) && aligned16(a.part[0]) && aligned16(a.part[1]) &&
+                      aligned16(a.part[2]);
+  const void* fn;
+  if (vec_ok) fn = pack ? (const void*)qkv_pack_kernel<T, VMAX, true> : (const void*)qkv_pack_kernel<T, VMAX, false>;
+  else fn = pack ? (const void*)qkv_pack_kernel<T, 1, true> : (const void*)qkv_pack_kernel<T, 1, false>;
+  return launch(fn, &a, a.rows, threads_for(vec_ok ? a.hidden / VMAX : a.hidden), st);
+}
+
+static int qkv_entry(int dtype, bool pack, void* qkv, void* q, void* k, void* v, int64_t rows, int64_t hidden,
+                     void* stream) {
+  if (rows < 0 || hidden <= 0) return ND_ERR_BAD_ARG;
+  if (hidden > INT32_MAX / 3) return ND_ERR_UNSUPPORTED;
+  if (rows == 0) return ND_OK;
+  if (!qkv || !q || !k || !v) return ND_ERR_BAD_ARG;
+  QkvArgs a{qkv, {q, k, v}, rows, static_cast<int>(hidden)};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case ND_F16: return launch_qkv<__half>(a, pack, st);
+    case ND_BF16: return launch_qkv<__nv_bfloat16>(a, pack, st);
+    case ND_F32: return launch_qkv<float>(a, pack, st);
+    default: return ND_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace nd
+
+extern "C" {
+
+int nd_out_residual_fwd(int dtype, const void* x, const void* residual, const void* bias, void* y, int64_t rows,
+                        int64_t hidden, void* stream) {
+  using namespace nd;
+  if (rows < 0 || hidden <= 0) return ND_ERR_BAD_ARG;
+  if (hidden > INT32_MAX) return ND_ERR_UNSUPPORTED;
+  if (rows == 0) return ND_OK;
+  if (!x || !residual || !y) return ND_ERR_BAD_ARG;
+  ResidualArgs a{x, residual, bias, y, rows, static_cast<int>(hidden)};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case ND_F16: return launch_residual<__half>(a, st);
+    case ND_BF16: return launch_residual<__nv_bfloat16>(a, st);
+    case ND_F32: return launch_residual<float>(a, st);
+    default: return ND_ERR_UNSUPPORTED;
+  }
+}
+
+int nd_qkv_pack_fwd(int dtype, const void* qkv, void* q, void* k, void* v, int64_t rows, int64_t hidden,
+                    void* stream) {
+  return nd::qkv_entry(dtype, true, const_cast<void*>(qkv), q, k, v, rows, hidden, stream);
+}
+
+int nd_qkv_pack_bwd(int dtype, const void* dq, const void* dk, const void* dv, void* dqkv, int64_t rows,
+                    int64_t hidden, void* stream) {
+  return nd::qkv_entry(dtype, false, dqkv, const_cast<void*>(dq), const_cast<void*>(dk), const_cast<void*>(dv), rows,
+                       hidden, stream);
+}
+
+}  // extern "C"

@@ -261,6 +261,25 @@ at::Tensor fused_gate_act_backward(const at::Tensor& dy, const at::Tensor& x, in
   return dz;
 }
 
+// Activation backward of FC1's pre-activation z [B, S, 2I] = [gate | value] (no counterpart in the reference's
+// extension: its autograd Function does this step in eager PyTorch, novadit/ops/fc1_bias_act.py:255-270).
+at::Tensor fused_gate_act_backward_gate_first(const at::Tensor& dy, const at::Tensor& z, int64_t act_id) {
+  check_gate_act_inputs(z);
+  TORCH_CHECK(act_id == 0 || act_id == 1, "act_id must be 0 (SiLU) or 1 (GELU), got ", act_id);
+  TORCH_CHECK(dtype_id(z) >= 0, "fused_gate_act_backward_gate_first only supports fp32/fp16/bf16 tensors");
+  TORCH_CHECK(dy.is_cuda(), "dy must be a CUDA tensor");
+  TORCH_CHECK(dy.dim() == 3 && dy.size(0) == z.size(0) && dy.size(1) == z.size(1) && dy.size(2) * 2 == z.size(2),
+              "dy must have shape [B, S, I]");
+  TORCH_CHECK(dy.scalar_type() == z.scalar_type(), "dy and z must have the same dtype");
+  c10::cuda::CUDAGuard guard(z.device());
+  at::Tensor dy_c = dy.contiguous();
+  at::Tensor dz = at::empty_like(z);
+  check_status(nd_gate_act_bwd_gate_first(dtype_id(z), static_cast<int>(act_id), dy_c.data_ptr(), z.data_ptr(),
+                                          dz.data_ptr(), z.size(0) * z.size(1), z.size(2) / 2, current_stream(z)),
+               "fused_gate_act_backward_gate_first");
+  return dz;
+}
+
 at::Tensor fused_geglu_forward(const at::Tensor& z) { return fused_gate_act_forward(z, ND_ACT_GELU); }
 at::Tensor fused_geglu_backward(const at::Tensor& dy, const at::Tensor& z) {
   return fused_gate_act_backward(dy, z, ND_ACT_GELU);
@@ -317,13 +336,65 @@ at::Tensor fused_fc1_bias_act_forward_plain(const at::Tensor& x, const at::Tenso
   return fc1_forward(x, weight, bias, act_id, 0);
 }
 
-// ------------------------------------------------------------------ not on this path
-// csrc/ops/qkv_pack_kernel.cu:5-10 and csrc/ops/residual_kernel.cu:3-8 raise in the reference too.
-std::vector<at::Tensor> fused_qkv_pack_forward(const at::Tensor&, int64_t, int64_t) {
-  TORCH_CHECK(false, "fused_qkv_pack_forward is scaffolded but not implemented yet");
+// ------------------------------------------------------------------ row operators next to the path
+// The reference binds these two names (csrc/bindings.cpp:91-96) to kernels that raise
+// (csrc/ops/qkv_pack_kernel.cu:5-10, csrc/ops/residual_kernel.cu:3-8); here they run.
+std::vector<at::Tensor> fused_qkv_pack_forward(const at::Tensor& qkv, int64_t num_heads, int64_t head_dim) {
+  TORCH_CHECK(qkv.is_cuda(), "qkv must be a CUDA tensor");
+  TORCH_CHECK(qkv.dim() == 3, "qkv must have shape [B, S, 3 * num_heads * head_dim]");
+  TORCH_CHECK(num_heads > 0 && head_dim > 0, "num_heads and head_dim must be positive");
+  const int64_t hidden = num_heads * head_dim;
+  TORCH_CHECK(qkv.size(2) == 3 * hidden, "Expected last dim ", 3 * hidden, ", got ", qkv.size(2));
+  TORCH_CHECK(dtype_id(qkv) >= 0, "fused_qkv_pack_forward only supports fp32/fp16/bf16 tensors");
+  c10::cuda::CUDAGuard guard(qkv.device());
+  at::Tensor src = qkv.contiguous();
+  std::vector<at::Tensor> out;
+  for (int i = 0; i < 3; ++i) out.push_back(at::empty({qkv.size(0), qkv.size(1), num_heads, head_dim}, qkv.options()));
+  check_status(nd_qkv_pack_fwd(dtype_id(qkv), src.data_ptr(), out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(),
+                               qkv.size(0) * qkv.size(1), hidden, current_stream(qkv)),
+               "fused_qkv_pack_forward");
+  return out;
 }
-at::Tensor fused_out_residual_forward(const at::Tensor&, const at::Tensor&, c10::optional<at::Tensor>) {
-  TORCH_CHECK(false, "fused_out_residual_forward is scaffolded but not implemented yet");
+
+// backward of the pack: dq, dk, dv [B, S, heads, head_dim] -> dqkv [B, S, 3 * hidden] (added; not in the reference)
+at::Tensor fused_qkv_pack_backward(const at::Tensor& dq, const at::Tensor& dk, const at::Tensor& dv) {
+  TORCH_CHECK(dq.is_cuda() && dk.is_cuda() && dv.is_cuda(), "dq, dk, dv must be CUDA tensors");
+  TORCH_CHECK(dq.dim() == 4 && dq.sizes() == dk.sizes() && dq.sizes() == dv.sizes(),
+              "dq, dk, dv must have the same shape [B, S, num_heads, head_dim]");
+  TORCH_CHECK(dq.scalar_type() == dk.scalar_type() && dq.scalar_type() == dv.scalar_type(), "dq, dk, dv must have one dtype");
+  TORCH_CHECK(dtype_id(dq) >= 0, "fused_qkv_pack_backward only supports fp32/fp16/bf16 tensors");
+  c10::cuda::CUDAGuard guard(dq.device());
+  at::Tensor q = dq.contiguous(), k = dk.contiguous(), v = dv.contiguous();
+  const int64_t hidden = dq.size(2) * dq.size(3);
+  at::Tensor dqkv = at::empty({dq.size(0), dq.size(1), 3 * hidden}, dq.options());
+  check_status(nd_qkv_pack_bwd(dtype_id(dq), q.data_ptr(), k.data_ptr(), v.data_ptr(), dqkv.data_ptr(),
+                               dq.size(0) * dq.size(1), hidden, current_stream(dq)),
+               "fused_qkv_pack_backward");
+  return dqkv;
+}
+
+at::Tensor fused_out_residual_forward(const at::Tensor& x, const at::Tensor& residual, c10::optional<at::Tensor> bias) {
+  TORCH_CHECK(x.is_cuda() && residual.is_cuda(), "x and residual must be CUDA tensors");
+  TORCH_CHECK(x.dim() == 3, "x must have shape [B, S, H]");
+  TORCH_CHECK(residual.sizes() == x.sizes(), "residual must have the same shape as x");
+  TORCH_CHECK(residual.scalar_type() == x.scalar_type(), "x and residual must have the same dtype");
+  TORCH_CHECK(dtype_id(x) >= 0, "fused_out_residual_forward only supports fp32/fp16/bf16 tensors");
+  const void* bias_p = nullptr;
+  at::Tensor bias_c;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_cuda(), "bias must be a CUDA tensor");
+    TORCH_CHECK(bias->numel() == x.size(2), "bias must have H elements");
+    TORCH_CHECK(bias->scalar_type() == x.scalar_type(), "bias dtype must match x dtype");
+    bias_c = bias->contiguous();
+    bias_p = bias_c.data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor xc = x.contiguous(), rc = residual.contiguous();
+  at::Tensor y = at::empty_like(xc);
+  check_status(nd_out_residual_fwd(dtype_id(x), xc.data_ptr(), rc.data_ptr(), bias_p, y.data_ptr(),
+                                   x.size(0) * x.size(1), x.size(2), current_stream(x)),
+               "fused_out_residual_forward");
+  return y;
 }
 
 }  // namespace
@@ -334,12 +405,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fused_adaln_backward_dx", &fused_adaln_backward_dx, "fused AdaLN backward dx");
   m.def("fused_adaln_backward_dparam", &fused_adaln_backward_dparam, "fused AdaLN backward -> [dscale, dshift] fp32");
   m.def("fused_adaln_backward", &fused_adaln_backward, "one-pass AdaLN backward -> [dx, dscale, dshift]");
-  m.def("fused_qkv_pack_forward", &fused_qkv_pack_forward, "not implemented (as in the reference)");
-  m.def("fused_out_residual_forward", &fused_out_residual_forward, "not implemented (as in the reference)");
+  m.def("fused_qkv_pack_forward", &fused_qkv_pack_forward, "qkv [B,S,3H] -> [q, k, v], each [B,S,heads,head_dim]");
+  m.def("fused_qkv_pack_backward", &fused_qkv_pack_backward, "dq, dk, dv [B,S,heads,head_dim] -> dqkv [B,S,3H]");
+  m.def("fused_out_residual_forward", &fused_out_residual_forward, "y = x + residual (+ bias)");
   m.def("fused_geglu_forward", &fused_geglu_forward, "fused GeGLU forward (GELU-gated, tanh approx)");
   m.def("fused_geglu_backward", &fused_geglu_backward, "fused GeGLU backward");
   m.def("fused_gate_act_forward", &fused_gate_act_forward, "fused gate-act forward (act_id: 0=SiLU, 1=GELU)");
   m.def("fused_gate_act_backward", &fused_gate_act_backward, "fused gate-act backward (act_id: 0=SiLU, 1=GELU)");
+  m.def("fused_gate_act_backward_gate_first", &fused_gate_act_backward_gate_first,
+        "gate-act backward for rows [gate | value] (FC1 pre-activation)");
   m.def("fused_adarmsnorm_forward", &fused_adarmsnorm_forward, "fused AdaRMSNorm forward -> [y, scale, inv_rms]");
   m.def("fused_adarmsnorm_forward_inference", &fused_adarmsnorm_forward_inference, "fused AdaRMSNorm forward, y only");
   m.def("fused_adarmsnorm_backward_dx", &fused_adarmsnorm_backward_dx, "fused AdaRMSNorm backward dx");

@@ -55,15 +55,9 @@ from .fc1_bias_act import (  # noqa: E402
     un_interleave_weight,
 )
 from .gate_act import fused_gate_act, fused_geglu, gate_act_ref, geglu_ref  # noqa: E402
-from .outside_path import (  # noqa: E402
-    adaln_compile,
-    adarmsnorm_compile,
-    fused_out_residual,
-    fused_qkv_linear_pack,
-    fused_qkv_pack,
-    out_residual_ref,
-    qkv_pack_ref,
-)
+from .outside_path import adaln_compile, adarmsnorm_compile  # noqa: E402
+from .qkv_pack import fused_qkv_linear_pack, fused_qkv_pack, qkv_pack_ref  # noqa: E402
+from .residual import fused_out_residual, out_residual_ref  # noqa: E402
 
 __all__ = [
     "HAS_NOVADIT_CUDA",

@@ -95,3 +95,16 @@ def test_extreme_gate_values_do_not_produce_nan():
         assert torch.isfinite(y).all() and torch.isfinite(dz).all()
         torch.testing.assert_close(y, oracle.gate_act_fwd(x, act, compute=torch.float64), rtol=1e-4, atol=1e-4)
         torch.testing.assert_close(dz, oracle.gate_act_bwd(dy, x, act, compute=torch.float64), rtol=5e-4, atol=5e-4)
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+@pytest.mark.parametrize("dtype,inter", [(torch.bfloat16, 4608), (torch.float16, 200), (torch.float32, 33)])
+def test_gate_first_layout_is_the_same_backward_with_halves_swapped(act, dtype, inter):
+    """Rows [gate | up] (FC1's pre-activation) give, half for half, the bits of the [up | gate] backward."""
+    x, dy = synth.gate_act_inputs(2, 37, inter, dtype, seed=9)
+    xd, gd = x.to(DEV), dy.to(DEV)
+    dz = capi.gate_act_bwd(gd, xd, act)
+    z = torch.cat([xd[..., inter:], xd[..., :inter]], dim=-1).contiguous()
+    dz_gf = capi.gate_act_bwd(gd, z, act, gate_first=True)
+    torch.cuda.synchronize()
+    assert torch.equal(dz_gf[..., :inter], dz[..., inter:]) and torch.equal(dz_gf[..., inter:], dz[..., :inter])

@@ -60,9 +60,9 @@ def test_extension_validates_like_the_reference():
         ext.fused_adaln_forward(x, torch.randn(2, 16), torch.randn(2, 16), 1e-5)
     with pytest.raises(RuntimeError, match="z must be a CUDA tensor"):
         ext.fused_geglu_forward(x)
-    with pytest.raises(RuntimeError, match="not implemented"):
+    with pytest.raises(RuntimeError, match="qkv must be a CUDA tensor"):
         ext.fused_qkv_pack_forward(x, 2, 8)
-    with pytest.raises(RuntimeError, match="not implemented"):
+    with pytest.raises(RuntimeError, match="must be CUDA tensors"):
         ext.fused_out_residual_forward(x, x, None)
 
 
