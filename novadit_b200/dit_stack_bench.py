@@ -93,7 +93,7 @@ def main() -> None:
         yr, gr = ref_step()
 
         def rel(a, b):
-            a, b = a.float(), b.float()
+            a, b = a.detach().float(), b.detach().float()
             return float((a - b).norm() / b.norm().clamp_min(1e-30))
 
         result["parity_vs_pytorch_stack"] = {

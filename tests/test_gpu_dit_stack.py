@@ -11,7 +11,7 @@ DEV = "cuda"
 
 
 def rel_l2(a, b):
-    a, b = a.float(), b.float()
+    a, b = a.detach().float(), b.detach().float()
     return float((a - b).norm() / b.norm().clamp_min(1e-30))
 
 

@@ -31,7 +31,7 @@ def test_out_residual(dtype, shape, with_bias):
         assert rel_l2(y, want) < 1e-6
     else:
         # one rounding of the (exact in fp32) sum: within half a unit in the last place of the exact value
-        half_ulp = 2.0 ** -9 if dtype == torch.bfloat16 else 2.0 ** -12
+        half_ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11  # relative to the value, at most
         err = (y.cpu().double() - want).abs()
         assert bool((err <= half_ulp * want.abs() * 1.001 + 1e-7).all()) and rel_l2(y, want) < HALF_REL_L2
         # ... so at least as close to the exact sum as the reference's two roundings
