@@ -41,7 +41,7 @@ enum {
 enum { ND_F16 = 0, ND_BF16 = 1, ND_F32 = 2, ND_E4M3 = 3 };
 
 /* activation ids: csrc/common/dispatch.h:7-10 (kSilu = 0, kGelu = 1; GELU is the tanh form) */
-enum { ND_ACT_SILU = 0, ND_ACT_GELU = 1 };
+enum { ND_ACT_SILU = 0, ND_ACT_GELU = 1, ND_ACT_NONE = 2 /* identity: nd_fc1_fwd with gated == 0 only */ };
 
 const char* nd_status_string(int status);
 /* cudaError_t of the last failed launch on the calling thread (0 if none) */
@@ -202,7 +202,10 @@ int nd_qkv_pack_bwd(int dtype, const void* dq, const void* dk, const void* dv, v
  *               y [m, n/2] = value * act(gate)  (layout of novadit/ops/fc1_bias_act.py:55-68).
  *   gated == 2: same function, rows interleaved (gate0, value0, gate1, ...): the layout
  *               fused_fc1_bias_act_forward receives from novadit/ops/fc1_bias_act.py:237-239.
- *   gated == 0: y [m, n] = act(z).
+ *   gated == 0: y [m, n] = act(z); with act == ND_ACT_NONE a plain GEMM + bias, which is how the
+ *               backward dx = dz @ W of the reference's FC1GatedActSM120BF16BackwardDxKernel
+ *               (csrc/cute_dsl/fc1_bias_act/fc1_bias_act.py:996-1913, called from
+ *               novadit/ops/fc1_bias_act.py:288-326) runs here: x := dz, w := W^T.
  * ab_dtype: ND_BF16, ND_F16 or ND_E4M3 (both operands); out_dtype: ND_BF16 or ND_F16, also the
  * dtype of `bias` (nullable, length n). alpha = alpha_host * (alpha_dev ? alpha_dev[0] *
  * alpha_dev[1] : 1): pass the two per-tensor de-quantisation scales of an FP8 call as a
@@ -215,6 +218,15 @@ int nd_qkv_pack_bwd(int dtype, const void* dq, const void* dk, const void* dv, v
 int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const void* x, const void* w,
                const void* bias, float alpha_host, const float* alpha_dev, void* y, int64_t m,
                int64_t k, int64_t n, int* status, void* stream);
+
+/* Backward of the fused FC1 with respect to its pre-activation, recomputation included:
+ * dz [m, n] = [dy * value * act'(gate) | dy * act(gate)] with [gate | value] = x @ w^T + bias for w rows
+ * [gate block | value block] (gated == 1 of nd_fc1_fwd), dy [m, n/2]. One launch of the forward
+ * kernel's main loop with the activation backward as epilogue; z is never written. dtype ND_BF16 or
+ * ND_F16 for x, w, bias, dy and dz. Replaces F.linear + the eager activation backward of
+ * novadit/ops/fc1_bias_act.py:255-270. `status` as in nd_fc1_fwd. */
+int nd_fc1_bwd_dz(int dtype, int act, const void* x, const void* w, const void* bias, const void* dy,
+                  void* dz, int64_t m, int64_t k, int64_t n, int* status, void* stream);
 
 /* Tuning hook for the gate-act kernels: rows per CTA group (1, 2 or 4; 0 = default) and 1 = a single
  * resident wave of CTAs striding over the groups instead of one CTA per group (default 0). Process-wide.

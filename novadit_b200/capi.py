@@ -17,7 +17,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libnovadit_
 
 ND_F16, ND_BF16, ND_F32, ND_E4M3 = 0, 1, 2, 3
 ACT_SILU, ACT_GELU = 0, 1
-ACT_IDS = {"silu": ACT_SILU, "gelu": ACT_GELU}
+ACT_IDS = {"silu": ACT_SILU, "gelu": ACT_GELU, "none": 2}
 DTYPE_IDS = {torch.float16: ND_F16, torch.bfloat16: ND_BF16, torch.float32: ND_F32,
              torch.float8_e4m3fn: ND_E4M3}
 
@@ -64,6 +64,8 @@ SIGNATURES = {
     "nd_qkv_pack_bwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "nd_fc1_fwd": (c_int, [c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float,
                            c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "nd_fc1_bwd_dz": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                              c_int64, c_void_p, c_void_p]),
     "nd_tune_gate_act": (None, [c_int, c_int]),
     "nd_tune_fc1_pair": (None, [c_int]),
     "nd_tune_fc1_trace": (None, [c_void_p]),
@@ -262,6 +264,18 @@ def fc1_fwd(x, w, bias=None, act="silu", gated=True, *, alpha=1.0, alpha_dev=Non
                            _ptr(bias), float(alpha), _ptr(alpha_dev), _ptr(y), m, k, n, _ptr(status), _stream()),
           "nd_fc1_fwd")
     return y
+
+
+def fc1_bwd_dz(x, w, bias, dy, act="silu", status=None):
+    """dz [..., N] of the gated FC1 (w rows [gate | value]) from x, w, bias and dy [..., N/2], z recomputed inside."""
+    _need_cuda(x, w, bias, dy)
+    k = x.shape[-1]
+    m = x.numel() // k
+    n = w.shape[0]
+    dz = torch.empty(*x.shape[:-1], n, dtype=x.dtype, device=x.device)
+    check(lib().nd_fc1_bwd_dz(DTYPE_IDS[x.dtype], ACT_IDS[act], _ptr(x), _ptr(w), _ptr(bias), _ptr(dy), _ptr(dz),
+                              m, k, n, _ptr(status), _stream()), "nd_fc1_bwd_dz")
+    return dz
 
 
 _AMAX_WS: dict = {}

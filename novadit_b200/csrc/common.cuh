@@ -193,7 +193,9 @@ constexpr float kGeluE0 = -2.f * 1.4426950408889634f * kGeluC0;
 constexpr float kGeluE1 = kGeluE0 * kGeluC1;
 
 template <int ACT> __device__ __forceinline__ float act_fwd(float g) {
-  if constexpr (ACT == ND_ACT_SILU) {
+  if constexpr (ACT == ND_ACT_NONE) {
+    return g;
+  } else if constexpr (ACT == ND_ACT_SILU) {
     return g * sigmoid_f32(g);
   } else {
     return g * sigmoid_from_exp2arg(g * fmaf(kGeluE1, g * g, kGeluE0));

@@ -53,17 +53,24 @@ struct Fc1Args {
   int tiles_m, tiles_n, k_blocks;
 };
 
-struct __align__(1024) Fc1Smem {
-  uint8_t stage[kStages][kStageBytes];
-  uint8_t out[kEpilogueWarps][kOutBlockBytes];  // output staging, one 32 x 32 block per epilogue warp
+constexpr int kBwdStages = 3;  // the backward-dz variant trades one operand stage for two more epilogue blocks
+
+// STAGES operand stages; BLOCKS 32 x 32 staging blocks per epilogue warp (1: output; 3: dy in, two dz halves out)
+template <int STAGES, int BLOCKS>
+struct __align__(1024) Fc1SmemT {
+  uint8_t stage[STAGES][kStageBytes];
+  uint8_t out[kEpilogueWarps][BLOCKS][kOutBlockBytes];  // staging, private to each epilogue warp
   alignas(16) float bias[kEpilogueWarps][kBN];  // one private copy per epilogue warp: no cross-warp barrier in the epilogue
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t dy_full[kEpilogueWarps];  // backward: the warp's dy block has landed
   uint32_t tmem_base;
   int abort_flag;
 };
+using Fc1Smem = Fc1SmemT<kStages, 1>;
+using Fc1BwdSmem = Fc1SmemT<kBwdStages, 3>;
 
 // Bounded wait. Returns false if the CTA is aborting or the limit expired (and raises the abort).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
@@ -154,6 +161,14 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
 template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
   __half2 v = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <typename OUT> __device__ __forceinline__ float2 unpack_pair(uint32_t w);
+template <> __device__ __forceinline__ float2 unpack_pair<__nv_bfloat16>(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 unpack_pair<__half>(uint32_t w) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
 }
 
 // Bias of the tile's 256 accumulator columns -> one epilogue warp's shared-memory copy (fp32).
@@ -267,6 +282,91 @@ __device__ __forceinline__ void epilogue_columns(const Fc1Args& a, const CUtenso
   }
 }
 
+// Backward of the gated activation in the epilogue (stacked gating only): the accumulators are the recomputed
+// pre-activations z = x W^T + b of the tile, and with the 32 x 32 block of dy fetched by the copy engine into
+// the warp's first staging block,
+//   dz[:, c]         = dy * value * act'(gate)     (gate half)
+//   dz[:, n_out + c] = dy * act(gate)              (value half)
+// leave through the other two blocks as two block stores. z itself never reaches memory.
+template <int ACT, typename OUT>
+__device__ __forceinline__ void epilogue_columns_bwd(const Fc1Args& a, const CUtensorMap* map_dy,
+                                                     const CUtensorMap* map_dzg, const CUtensorMap* map_dzv,
+                                                     const float* sb, uint8_t* blocks,
+                                                     uint64_t* dy_bar, uint32_t& dy_phase, volatile int* abort_flag,
+                                                     uint32_t t_lane, int row0, int ni, int colhalf, float alpha, int lane,
+                                                     bool& ok) {
+  const int out0 = ni * 128;
+  const float4* sb4 = reinterpret_cast<const float4*>(sb);
+  uint8_t* blk_dy = blocks;
+  uint8_t* blk_g = blocks + kOutBlockBytes;
+  uint8_t* blk_v = blocks + 2 * kOutBlockBytes;
+  const int sw = (lane >> 1) & 3;
+#pragma unroll 1
+  for (int ch = colhalf * 2; ch < colhalf * 2 + 2; ++ch) {
+    const int col = out0 + ch * 32;
+    if (lane == 0) {  // rows and columns outside dy are filled with zeros, the byte count is always the full block
+      mbar_expect_tx(dy_bar, kOutBlockBytes);
+      tma_load_2d(blk_dy, map_dy, dy_bar, col, row0);
+    }
+    float g[32], v[32];
+    tc_ld32(t_lane + ch * 32, g);
+    tc_ld32(t_lane + 128 + ch * 32, v);
+    tc_wait_ld();
+    ok = __all_sync(0xffffffffu, mbar_wait(dy_bar, dy_phase, abort_flag, a.status, 5));
+    if (!ok) return;
+    dy_phase ^= 1u;
+    float dyv[32];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint4 pk = *reinterpret_cast<const uint4*>(blk_dy + lane * 64 + ((c ^ sw) << 4));
+      const uint32_t w4[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_pair<OUT>(w4[e]);
+        dyv[c * 8 + 2 * e] = f.x;
+        dyv[c * 8 + 2 * e + 1] = f.y;
+      }
+    }
+    float dg[32], dv[32];
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+      const float4 bg = sb4[ch * 8 + j4], bv = sb4[32 + ch * 8 + j4];
+      const float bgs[4] = {bg.x, bg.y, bg.z, bg.w}, bvs[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = j4 * 4 + e;
+        float grad;
+        const float av = act_fwd_grad<ACT>(fmaf(g[j], alpha, bgs[e]), grad);
+        dv[j] = dyv[j] * av;
+        dg[j] = dyv[j] * fmaf(v[j], alpha, bvs[e]) * grad;
+      }
+    }
+    if (lane == 0) bulk_wait_read_all();  // the previous step's stores have left the two output blocks
+    __syncwarp();
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint4 pg, pv;
+      pg.x = pack2<OUT>(dg[c * 8 + 0], dg[c * 8 + 1]);
+      pg.y = pack2<OUT>(dg[c * 8 + 2], dg[c * 8 + 3]);
+      pg.z = pack2<OUT>(dg[c * 8 + 4], dg[c * 8 + 5]);
+      pg.w = pack2<OUT>(dg[c * 8 + 6], dg[c * 8 + 7]);
+      pv.x = pack2<OUT>(dv[c * 8 + 0], dv[c * 8 + 1]);
+      pv.y = pack2<OUT>(dv[c * 8 + 2], dv[c * 8 + 3]);
+      pv.z = pack2<OUT>(dv[c * 8 + 4], dv[c * 8 + 5]);
+      pv.w = pack2<OUT>(dv[c * 8 + 6], dv[c * 8 + 7]);
+      *reinterpret_cast<uint4*>(blk_g + lane * 64 + ((c ^ sw) << 4)) = pg;
+      *reinterpret_cast<uint4*>(blk_v + lane * 64 + ((c ^ sw) << 4)) = pv;
+    }
+    fence_proxy_async_smem();
+    __syncwarp();  // also: every lane has read its dy before the next step's copy may overwrite the block
+    if (lane == 0 && row0 < a.m && col < a.n_out) {
+      tma_store_2d(map_dzg, blk_g, col, row0);
+      tma_store_2d(map_dzv, blk_v, col, row0);
+      bulk_commit();
+    }
+  }
+}
+
 // ------------------------------------------------------------------ the MMA issuer
 // tcgen05.mma with the operand descriptors given as (low word, shared high word): only the 14-bit start
 // address in the low word differs between stages and K slices, so the issuing thread keeps one register per
@@ -354,19 +454,25 @@ __device__ __forceinline__ void mma_issue_loop(uint32_t stage0_addr, uint64_t* f
 
 // ABF: instruction-descriptor operand format (kind::f16: 0 = f16, 1 = bf16; kind::f8f6f4: 0 = e4m3)
 // GATED: 0 = y = act(z); 1 = w rows [gate block | value block]; 2 = w rows interleaved (gate0, value0, gate1, ...)
-template <bool F8, int ABF, int GATED, int ACT, typename OUT>
+// BWD: the epilogue is the activation backward (map_y / map_y2 describe the gate / value half of dz, each as its
+// own [m, n_out] tensor so that the copy engine clips a block at the half's edge; map_dy the incoming gradient)
+template <bool F8, int ABF, int GATED, int ACT, typename OUT, bool BWD = false>
 __global__ void __launch_bounds__(kThreads, 1)
 fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-           const __grid_constant__ CUtensorMap map_y, const Fc1Args a) {
+           const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_y2,
+           const __grid_constant__ CUtensorMap map_dy, const Fc1Args a) {
+  static_assert(!BWD || (GATED == 1 && !F8), "the backward epilogue exists for stacked gating and 16-bit operands");
+  constexpr int kS = BWD ? kBwdStages : kStages;
+  using Smem = Fc1SmemT<kS, BWD ? 3 : 1>;
   extern __shared__ uint8_t smem_raw[];
-  Fc1Smem& s = *reinterpret_cast<Fc1Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &s.abort_flag;
   constexpr int kBKElems = F8 ? 128 : 64;
   const int total_tiles = a.tiles_m * a.tiles_n;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kStages; ++i) {
+    for (int i = 0; i < kS; ++i) {
       mbar_init(&s.full[i], 1);
       mbar_init(&s.empty[i], 1);
     }
@@ -374,6 +480,7 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
       mbar_init(&s.tmem_full[i], 1);
       mbar_init(&s.tmem_empty[i], kEpilogueWarps);
     }
+    for (int i = 0; i < kEpilogueWarps; ++i) mbar_init(&s.dy_full[i], 1);
     s.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_x)) : "memory");
@@ -415,7 +522,7 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
           tma_load_2d(base, &map_x, &s.full[stage], kb * kBKElems, m0);
           tma_load_2d(base + kATileBytes, &map_w, &s.full[stage], kb * kBKElems, nb0);
           tma_load_2d(base + kATileBytes + kBHalfBytes, &map_w, &s.full[stage], kb * kBKElems, nb1);
-          if (++stage == kStages) {
+          if (++stage == kS) {
             stage = 0;
             phase ^= 1u;
           }
@@ -438,7 +545,7 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
     if (lane == 0) {
       const int my_tiles =
           static_cast<int>(blockIdx.x) < total_tiles ? (total_tiles - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1 : 0;
-      mma_issue_loop<F8, false, kStages, kStageBytes>(smem_u32(s.stage[0]), s.full, s.empty, s.tmem_full, s.tmem_empty,
+      mma_issue_loop<F8, false, kS, kStageBytes>(smem_u32(s.stage[0]), s.full, s.empty, s.tmem_full, s.tmem_empty,
                                                        tmem_base, umma_idesc(ABF), my_tiles, a.k_blocks, abort_flag,
                                                        a.status, 2, 3);
     }
@@ -451,6 +558,7 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
     long long* tr3 = (a.trace != nullptr && lane == 0 && warp == 2) ? &w_tfull : nullptr;
     int acc = 0;
     uint32_t acc_phase = 0;
+    [[maybe_unused]] uint32_t dy_phase = 0;
     float alpha = a.alpha_host;
     if (a.alpha_dev != nullptr) alpha *= __ldg(a.alpha_dev) * __ldg(a.alpha_dev + 1);
     bool ok = true;
@@ -465,7 +573,13 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
       tc_fence_after();
       const int row0 = mi * kBM + q * 32;
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * kBN);
-      epilogue_columns<GATED, ACT, OUT>(a, &map_y, sb, s.out[warp - 2], t_lane, row0, ni, colhalf, alpha, lane);
+      if constexpr (BWD) {
+        epilogue_columns_bwd<ACT, OUT>(a, &map_dy, &map_y, &map_y2, sb, s.out[warp - 2][0], &s.dy_full[warp - 2], dy_phase,
+                                       abort_flag, t_lane, row0, ni, colhalf, alpha, lane, ok);
+        if (!ok) break;
+      } else {
+        epilogue_columns<GATED, ACT, OUT>(a, &map_y, sb, s.out[warp - 2][0], t_lane, row0, ni, colhalf, alpha, lane);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.tmem_empty[acc]);
@@ -732,6 +846,7 @@ static const void* pick_fc1(int act, int gated) {
     case 2:
       return silu ? (const void*)fc1_kernel<F8, ABF, 2, ND_ACT_SILU, OUT> : (const void*)fc1_kernel<F8, ABF, 2, ND_ACT_GELU, OUT>;
     default:
+      if (act == ND_ACT_NONE) return (const void*)fc1_kernel<F8, ABF, 0, ND_ACT_NONE, OUT>;
       return silu ? (const void*)fc1_kernel<F8, ABF, 0, ND_ACT_SILU, OUT> : (const void*)fc1_kernel<F8, ABF, 0, ND_ACT_GELU, OUT>;
   }
 }
@@ -745,6 +860,7 @@ static const void* pick_fc1_pair(int act, int gated) {
     case 2:
       return silu ? (const void*)fc1_pair_kernel<F8, ABF, 2, ND_ACT_SILU, OUT> : (const void*)fc1_pair_kernel<F8, ABF, 2, ND_ACT_GELU, OUT>;
     default:
+      if (act == ND_ACT_NONE) return (const void*)fc1_pair_kernel<F8, ABF, 0, ND_ACT_NONE, OUT>;
       return silu ? (const void*)fc1_pair_kernel<F8, ABF, 0, ND_ACT_SILU, OUT> : (const void*)fc1_pair_kernel<F8, ABF, 0, ND_ACT_GELU, OUT>;
   }
 }
@@ -769,7 +885,7 @@ extern "C" int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const
                           int64_t k, int64_t n, int* status, void* stream) {
   using namespace nd;
   if (m < 0 || k <= 0 || n <= 0) return ND_ERR_BAD_ARG;
-  if (act != ND_ACT_SILU && act != ND_ACT_GELU) return ND_ERR_UNSUPPORTED;
+  if (act != ND_ACT_SILU && act != ND_ACT_GELU && !(act == ND_ACT_NONE && gated == 0)) return ND_ERR_UNSUPPORTED;
   if (out_dtype != ND_BF16 && out_dtype != ND_F16) return ND_ERR_UNSUPPORTED;
   if (ab_dtype != ND_BF16 && ab_dtype != ND_F16 && ab_dtype != ND_E4M3) return ND_ERR_UNSUPPORTED;
   if (gated < 0 || gated > 2) return ND_ERR_BAD_ARG;
@@ -845,7 +961,9 @@ extern "C" int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const
     (void)cudaGetLastError();
     return ND_ERR_LAUNCH;
   }
-  void* params[] = {&map_x, &map_w, &map_y, &a};
+  void* params_single[] = {&map_x, &map_w, &map_y, &map_y, &map_y, &a};  // the forward epilogue uses the first of these only
+  void* params_pair[] = {&map_x, &map_w, &map_y, &a};
+  void** params = pair ? params_pair : params_single;
   cudaLaunchConfig_t cfg{};
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem_bytes;
@@ -873,6 +991,78 @@ extern "C" int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const
     cfg.gridDim = dim3(static_cast<unsigned>(grid));
   }
   e = cudaLaunchKernelExC(&cfg, fn, params);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    (void)cudaGetLastError();
+    return ND_ERR_LAUNCH;
+  }
+  return ND_OK;
+}
+
+// The reference's FC1 backward recomputes z = x W^T + b with F.linear, then differentiates the gated activation in
+// eager PyTorch (novadit/ops/fc1_bias_act.py:255-270). Here both happen in ONE launch of the forward kernel's main
+// loop with the activation backward as its epilogue: dz [m, n] = [dy * value * act'(gate) | dy * act(gate)] for
+// w rows [gate | value]; z never reaches memory. 16-bit operands, single-CTA tiles.
+extern "C" int nd_fc1_bwd_dz(int dtype, int act, const void* x, const void* w, const void* bias, const void* dy,
+                             void* dz, int64_t m, int64_t k, int64_t n, int* status, void* stream) {
+  using namespace nd;
+  if (m < 0 || k <= 0 || n <= 0 || (n % 2) != 0) return ND_ERR_BAD_ARG;
+  if (act != ND_ACT_SILU && act != ND_ACT_GELU) return ND_ERR_UNSUPPORTED;
+  if (dtype != ND_BF16 && dtype != ND_F16) return ND_ERR_UNSUPPORTED;
+  if (m == 0) return ND_OK;
+  if (!x || !w || !dy || !dz) return ND_ERR_BAD_ARG;
+  const long long n_out = n / 2;
+  if ((k * 2) % 16 != 0 || n_out % 8 != 0) return ND_ERR_UNSUPPORTED;
+  if (!aligned16(x) || !aligned16(w) || !aligned16(dy) || !aligned16(dz)) return ND_ERR_UNSUPPORTED;
+  if (m > INT32_MAX - kBM || n > INT32_MAX - kBN || k > INT32_MAX - 256) return ND_ERR_UNSUPPORTED;
+
+  Fc1Args a{};
+  a.bias = bias; a.y = dz; a.status = status; a.alpha_host = 1.f;
+  a.m = static_cast<int>(m); a.k = static_cast<int>(k); a.n = static_cast<int>(n);
+  a.n_out = static_cast<int>(n_out);
+  a.tiles_m = static_cast<int>((m + kBM - 1) / kBM);
+  a.tiles_n = static_cast<int>((n_out + 127) / 128);
+  a.k_blocks = static_cast<int>((k * 2 + kBKBytes - 1) / kBKBytes);
+  const long long tiles = static_cast<long long>(a.tiles_m) * a.tiles_n;
+  if (tiles > INT32_MAX) return ND_ERR_UNSUPPORTED;
+
+  const CUtensorMapDataType dt = dtype == ND_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap map_x, map_w, map_dzg, map_dzv, map_dy;
+  if (!make_map(&map_x, dt, 2, x, m, k) || !make_map(&map_w, dt, 2, w, n, k)) return ND_ERR_LAUNCH;
+  EncodeTiledFn enc = encode_fn();
+  if (enc == nullptr) return ND_ERR_LAUNCH;
+  // 32 x 32 blocks, 64-byte swizzle. The two halves of dz are described as separate [m, n_out] tensors with the row
+  // pitch of dz, so that a block that hangs over the end of the gate half is clipped instead of reaching into the
+  // value half.
+  auto block_map = [&](CUtensorMap* map, const void* base, long long cols, long long pitch_elems) {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(m)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * 2};
+    const cuuint32_t box[2] = {32u, 32u}, estr[2] = {1u, 1u};
+    return enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  };
+  const unsigned char* dzb = static_cast<const unsigned char*>(dz);
+  if (!block_map(&map_dzg, dzb, n_out, n) || !block_map(&map_dzv, dzb + n_out * 2, n_out, n) ||
+      !block_map(&map_dy, dy, n_out, n_out))
+    return ND_ERR_LAUNCH;
+  const void* fn;
+  if (dtype == ND_BF16)
+    fn = act == ND_ACT_SILU ? (const void*)fc1_kernel<false, 1, 1, ND_ACT_SILU, __nv_bfloat16, true>
+                            : (const void*)fc1_kernel<false, 1, 1, ND_ACT_GELU, __nv_bfloat16, true>;
+  else
+    fn = act == ND_ACT_SILU ? (const void*)fc1_kernel<false, 0, 1, ND_ACT_SILU, __half, true>
+                            : (const void*)fc1_kernel<false, 0, 1, ND_ACT_GELU, __half, true>;
+  const int smem_bytes = static_cast<int>(sizeof(Fc1BwdSmem)) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    (void)cudaGetLastError();
+    return ND_ERR_LAUNCH;
+  }
+  void* params[] = {&map_x, &map_w, &map_dzg, &map_dzv, &map_dy, &a};
+  const long long grid = tiles < sm_count() ? tiles : sm_count();
+  e = cudaLaunchKernel(fn, dim3(static_cast<unsigned>(grid)), dim3(kThreads), params, smem_bytes,
+                       static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) {
     set_last_cuda_error(e);
     (void)cudaGetLastError();

@@ -336,6 +336,56 @@ at::Tensor fused_fc1_bias_act_forward_plain(const at::Tensor& x, const at::Tenso
   return fc1_forward(x, weight, bias, act_id, 0);
 }
 
+// dz [B, S, 2I] from x [B, S, H], the FC1 weight [2I, H] (rows [gate | value]), its bias and dy [B, S, I]: the
+// recomputation of z and the activation backward of novadit/ops/fc1_bias_act.py:255-270 in one tcgen05 launch.
+at::Tensor fused_fc1_bias_act_backward_dz(const at::Tensor& x, const at::Tensor& weight, c10::optional<at::Tensor> bias,
+                                          const at::Tensor& dy, int64_t act_id) {
+  TORCH_CHECK(x.is_cuda() && weight.is_cuda() && dy.is_cuda(), "x, weight and dy must be CUDA tensors");
+  TORCH_CHECK(x.dim() == 3 && weight.dim() == 2 && weight.size(1) == x.size(2) && weight.size(0) % 2 == 0,
+              "x must be [batch, seq, hidden] and weight [2 * intermediate, hidden]");
+  TORCH_CHECK(dy.dim() == 3 && dy.size(0) == x.size(0) && dy.size(1) == x.size(1) && dy.size(2) * 2 == weight.size(0),
+              "dy must have shape [batch, seq, intermediate]");
+  TORCH_CHECK(x.scalar_type() == weight.scalar_type() && x.scalar_type() == dy.scalar_type(), "x, weight, dy: one dtype");
+  TORCH_CHECK(x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16, "fp16 and bf16 only");
+  TORCH_CHECK(act_id == 0 || act_id == 1, "act_id must be 0 (SiLU) or 1 (GELU)");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor xc = x.contiguous(), wc = weight.contiguous(), dyc = dy.contiguous(), bc;
+  const void* bias_p = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_cuda() && bias->numel() == weight.size(0) && bias->scalar_type() == x.scalar_type(),
+                "bias must be a CUDA tensor of 2 * intermediate elements with x's dtype");
+    bc = bias->contiguous();
+    bias_p = bc.data_ptr();
+  }
+  at::Tensor dz = at::empty({x.size(0), x.size(1), weight.size(0)}, x.options());
+  check_status(nd_fc1_bwd_dz(dtype_id(x), static_cast<int>(act_id), xc.data_ptr(), wc.data_ptr(), bias_p, dyc.data_ptr(),
+                             dz.data_ptr(), x.size(0) * x.size(1), x.size(2), weight.size(0), nullptr, current_stream(x)),
+               "fused_fc1_bias_act_backward_dz");
+  return dz;
+}
+
+// dx = dz @ weight for dz [B, S, 2I] and the FC1 weight [2I, H]: the job of the reference's CuTe-DSL backward-dx
+// kernel (csrc/cute_dsl/fc1_bias_act/fc1_bias_act.py:996-1913 behind novadit/ops/fc1_bias_act.py:288-326), run on
+// the tcgen05 GEMM of this library: the reduction runs over 2I, so the B operand is W^T [H, 2I], made K-major by
+// one transpose copy per call (the reference copies and transposes both weight halves per call, :309-315).
+at::Tensor fused_fc1_bias_act_backward_dx(const at::Tensor& dz, const at::Tensor& weight) {
+  TORCH_CHECK(dz.is_cuda() && weight.is_cuda(), "dz and weight must be CUDA tensors");
+  TORCH_CHECK(dz.dim() == 3, "dz must have shape [batch, seq, 2 * intermediate]");
+  TORCH_CHECK(weight.dim() == 2 && weight.size(0) == dz.size(2), "weight must have shape [2 * intermediate, hidden]");
+  TORCH_CHECK(dz.scalar_type() == weight.scalar_type(), "dz and weight must have the same dtype");
+  TORCH_CHECK(dz.scalar_type() == at::kHalf || dz.scalar_type() == at::kBFloat16,
+              "fused_fc1_bias_act_backward_dx supports fp16 and bf16 inputs");
+  c10::cuda::CUDAGuard guard(dz.device());
+  at::Tensor dzc = dz.contiguous();
+  at::Tensor wt = weight.t().contiguous();  // [H, 2I], reduction dimension contiguous
+  at::Tensor dx = at::empty({dz.size(0), dz.size(1), weight.size(1)}, dz.options());
+  check_status(nd_fc1_fwd(dtype_id(dz), dtype_id(dz), ND_ACT_NONE, /*gated=*/0, dzc.data_ptr(), wt.data_ptr(), nullptr,
+                          1.0f, nullptr, dx.data_ptr(), dz.size(0) * dz.size(1), dz.size(2), weight.size(1), nullptr,
+                          current_stream(dz)),
+               "fused_fc1_bias_act_backward_dx");
+  return dx;
+}
+
 // ------------------------------------------------------------------ row operators next to the path
 // The reference binds these two names (csrc/bindings.cpp:91-96) to kernels that raise
 // (csrc/ops/qkv_pack_kernel.cu:5-10, csrc/ops/residual_kernel.cu:3-8); here they run.
@@ -424,6 +474,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         "fused FC1 + bias + gated activation; weight/bias rows interleaved (gate0, value0, ...)");
   m.def("fused_fc1_bias_act_forward_stacked", &fused_fc1_bias_act_forward_stacked,
         "fused FC1 + bias + gated activation; weight rows [gate block | value block]");
+  m.def("fused_fc1_bias_act_backward_dz", &fused_fc1_bias_act_backward_dz,
+        "dz of the gated FC1 with z recomputed inside the kernel");
+  m.def("fused_fc1_bias_act_backward_dx", &fused_fc1_bias_act_backward_dx, "dx = dz @ weight on the tcgen05 GEMM");
   m.def("fused_fc1_bias_act_forward_plain", &fused_fc1_bias_act_forward_plain,
         "fused FC1 + bias + activation without gating, y = act(x W^T + b)");
 }

@@ -5,7 +5,9 @@ Mirrors the reference's `novadit/ops/fc1_bias_act.py` (reference function :55-68
 with the bias, activation and gating in its epilogue; the weight is consumed as stored (no
 per-call interleave copy, no JIT). The backward keeps the reference's formulation
 (novadit/ops/fc1_bias_act.py:248-285) - recompute z, activation backward, dx = dz W, dW = dz^T x - with the
-activation backward as one fused kernel over z's [gate | value] rows instead of eager PyTorch.
+recomputation and the activation backward in ONE tcgen05 launch (the forward main loop with a backward epilogue;
+z never reaches memory). dx, dW and dbias are library calls; the job of the reference's CuTe-DSL backward-dx
+kernel (:288-326) is also available on this library's tcgen05 GEMM as `fused_fc1_bias_act_backward_dx`.
 """
 from __future__ import annotations
 
@@ -66,10 +68,19 @@ class _FusedFc1BiasActFunction(torch.autograd.Function):
     def backward(ctx, dy):
         x, weight, bias = ctx.saved_tensors
         ext = require_cuda_extension("fused_fc1_bias_act", x, "fc1_bias_act_ref")
-        z = F.linear(x, weight, bias)  # recomputed, as in the reference: the forward kernel never writes it
-        dz = ext.fused_gate_act_backward_gate_first(dy.contiguous(), z, ctx.act_id)  # one pass instead of ~8 eager ones
+        inter, hidden = weight.shape[0] // 2, weight.shape[1]
+        if hidden % 8 == 0 and inter % 8 == 0:
+            # z recomputed and differentiated inside one tcgen05 launch: it never reaches memory
+            dz = ext.fused_fc1_bias_act_backward_dz(x, weight, bias, dy, ctx.act_id)
+        else:
+            z = F.linear(x, weight, bias)  # recomputed, as in the reference
+            dz = ext.fused_gate_act_backward_gate_first(dy.contiguous(), z, ctx.act_id)  # one pass, not ~8 eager ones
         m = x.shape[0] * x.shape[1]
         dz_flat, x_flat = dz.reshape(m, -1), x.reshape(m, -1)
+        # dx = dz W: a plain GEMM. `novadit_cuda.fused_fc1_bias_act_backward_dx` runs it on this library's tcgen05
+        # kernel (W^T made K-major by a transpose copy, as the reference's backward-dx kernel does), but at the
+        # DiT-XL/2 shape (M 8192, reduction 9216, 1152 outputs) its 256-wide tiles leave the last of three rounds
+        # 16 % full: 154 us + 48 us for the transpose against 123 us for the library GEMM, which is used here.
         dx = (dz_flat @ weight).reshape(x.shape)
         d_w = dz_flat.T @ x_flat
         d_b = dz_flat.sum(dim=0) if bias is not None else None
