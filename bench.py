@@ -305,8 +305,9 @@ def bench_e2e(dev, k: int) -> dict:
     steps on three streams. Every step's host->device and device->host copies are inside the timed region, which
     ends when the last step's results are in host memory."""
     from novadit_b200 import synth
-    from novadit_b200.hostpipe import HostPipeline, adaln_train_step
+    from novadit_b200.hostpipe import HostPipeline, adaln_train_step, bind_host_thread_to_gpu
 
+    bound = bind_host_thread_to_gpu(dev.index or 0)  # pinned buffers below land on the GPU's NUMA node
     host = [t.pin_memory() for t in synth.norm_inputs(B, S, H, torch.bfloat16, seed=0)]
     pipe = HostPipeline(adaln_train_step(EPS), dev, depth=3)
     for _ in range(12):  # untimed: pinned result buffers, allocator pools and copy paths reach their steady state
@@ -321,7 +322,7 @@ def bench_e2e(dev, k: int) -> dict:
     h2d = sum(t.numel() * t.element_size() for t in host)
     d2h = sum(t.numel() * t.element_size() for t in outs)
     return {"seconds_per_step": sec, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "pipeline": "3 streams, 3 steps in flight"}
+            "pipeline": "3 streams, 3 steps in flight", "host_thread_bound_to_gpu_numa_node": bound}
 
 
 def run_gpu_arm(args) -> None:
