@@ -307,6 +307,7 @@ def bench_e2e(dev, k: int) -> dict:
     from novadit_b200 import synth
     from novadit_b200.hostpipe import HostPipeline, adaln_train_step, bind_host_thread_to_gpu
 
+    cpus_before = os.sched_getaffinity(0)
     bound = bind_host_thread_to_gpu(dev.index or 0)  # pinned buffers below land on the GPU's NUMA node
     host = [t.pin_memory() for t in synth.norm_inputs(B, S, H, torch.bfloat16, seed=0)]
     pipe = HostPipeline(adaln_train_step(EPS), dev, depth=3)
@@ -319,6 +320,7 @@ def bench_e2e(dev, k: int) -> dict:
         pipe.submit(host)
     pipe.drain()
     sec = (time.perf_counter() - t0) / k
+    os.sched_setaffinity(0, cpus_before)  # the CPU baseline leg gets every core back
     h2d = sum(t.numel() * t.element_size() for t in host)
     d2h = sum(t.numel() * t.element_size() for t in outs)
     return {"seconds_per_step": sec, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
