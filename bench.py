@@ -256,6 +256,24 @@ def bench_extras(dev, stream, hbm_peak: float, tf_peak: float) -> dict:
                                  "frac_of_hbm_peak": rms_bytes / ms / 1e6 / hbm_peak}
     del rms, big
 
+    # the same step in eager PyTorch on this GPU (`adaln_ref` + autograd: what the reference runs on a GPU without its
+    # extension), over the same rotation of buffer sets
+    import novadit_b200.ops as ops
+
+    work = NormWorkload("layer", dev)
+
+    def eager_steps():
+        for st in work.sets:
+            xg, sg, hg = st["x"].requires_grad_(True), st["scale"].requires_grad_(True), st["shift"].requires_grad_(True)
+            torch.autograd.grad(ops.adaln_ref(xg, sg, hg, EPS), (xg, sg, hg), st["dy"])
+
+    for _ in range(2):
+        eager_steps()
+    torch.cuda.synchronize()
+    ms = event_time_ms(lambda: [eager_steps() for _ in range(3)], stream) / (3 * NSETS)
+    out["adaln_fwd_bwd_pytorch_eager_cuda"] = {"GB/s": STEP_BYTES / ms / 1e6, "ms_per_step": ms}
+    del work
+
     # gate-act, workload config 3: x [8, 4096, 2*4608] bf16 (604 MB, far larger than L2)
     rows, inter = 8 * 4096, 4608
     x, dy = synth.gate_act_inputs(1, 2048, inter, torch.bfloat16, seed=3)
