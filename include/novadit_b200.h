@@ -81,6 +81,20 @@ int nd_adaln_fwd(int dtype, const void* x, const void* scale, const void* shift,
                  float* mean, float* invstd, int64_t rows, int64_t row_start, int64_t seq_len,
                  int64_t hidden, float eps, void* stream);
 
+/* AdaLN / AdaRMSNorm forward with FP8 e4m3 OUTPUT for an FP8 consumer (nd_fc1_fwd with ND_E4M3 operands):
+ * q [rows, hidden] bytes = saturate_e4m3(y / *q_scale), statistics as in the 16-bit forward, and, when `amax` is
+ * not NULL, *amax = max(*amax, max |y|) over the launch (exact, order-independent). Delayed scaling: the caller
+ * passes the scale derived from an earlier step's maximum (amax / 448) and reads this step's maximum for the
+ * next one, so the activation never exists in 16 bits and no separate amax / quantise pass runs. q_scale and amax
+ * are device floats. Rows up to 192 16-byte vectors wide (hidden <= 1536 for 16-bit inputs), 16-byte aligned;
+ * anything else returns ND_ERR_UNSUPPORTED. No counterpart in the reference (it has no FP8 path). */
+int nd_adaln_fwd_e4m3(int dtype, const void* x, const void* scale, const void* shift, void* q, float* mean,
+                      float* invstd, const float* q_scale, float* amax, int64_t rows, int64_t row_start,
+                      int64_t seq_len, int64_t hidden, float eps, void* stream);
+int nd_adarms_fwd_e4m3(int dtype, const void* x, const void* scale, const void* shift, void* q,
+                       float* inv_rms, const float* q_scale, float* amax, int64_t rows, int64_t row_start,
+                       int64_t seq_len, int64_t hidden, float eps, void* stream);
+
 /* dx = invstd * (dxhat - mean_h(dxhat) - xhat * mean_h(dxhat * xhat)), dxhat = dy * (1 + scale[b]).
  * Replaces the launcher behind fused_adaln_backward_dx, csrc/ops/adaln_kernel.cu:1147-1193
  * (kernel :473-582). */
@@ -194,6 +208,20 @@ int nd_qkv_pack_fwd(int dtype, const void* qkv, void* q, void* k, void* v, int64
                     int64_t hidden, void* stream);
 int nd_qkv_pack_bwd(int dtype, const void* dq, const void* dk, const void* dv, void* dqkv,
                     int64_t rows, int64_t hidden, void* stream);
+
+/* Gated residual of adaLN-Zero DiT blocks (the harness of workload config 5; no counterpart in the reference,
+ * whose block has no gate): y = x + gate[b, :] * branch for rows of sample b = (row_start + r) / seq_len, gate
+ * [batch, hidden]. Backward: dbranch = gate * dy, and dgate_partials [samples_in_shard * tiles, hidden] fp32 =
+ * column sums of dy * branch per tile of `tile_rows` rows of a sample (tiles = ceil(seq_len / tile_rows)); the
+ * caller sums the tiles of a sample in order. dx of the residual is dy itself. nd_gated_residual_ws_bytes gives
+ * the size of the partials. */
+int nd_gated_residual_fwd(int dtype, const void* x, const void* branch, const void* gate, void* y, int64_t rows,
+                          int64_t row_start, int64_t seq_len, int64_t hidden, void* stream);
+size_t nd_gated_residual_ws_bytes(int64_t rows, int64_t row_start, int64_t seq_len, int64_t hidden,
+                                  int64_t tile_rows);
+int nd_gated_residual_bwd(int dtype, const void* dy, const void* branch, const void* gate, void* dbranch,
+                          float* dgate_partials, int64_t rows, int64_t row_start, int64_t seq_len,
+                          int64_t hidden, int64_t tile_rows, void* stream);
 
 /* -------------------------------------------------------------------- FC1 */
 

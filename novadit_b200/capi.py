@@ -54,6 +54,10 @@ SIGNATURES = {
                                      *_SHAPE4, c_void_p, c_size_t, c_void_p]),
     "nd_adarms_bwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_void_p, *_SHAPE4, c_void_p, c_size_t, c_void_p]),
+    "nd_adaln_fwd_e4m3": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, *_SHAPE4, c_float, c_void_p]),
+    "nd_adarms_fwd_e4m3": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   *_SHAPE4, c_float, c_void_p]),
     "nd_gate_act_fwd": (c_int, [c_int, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "nd_gate_act_bwd": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                 c_void_p]),
@@ -62,6 +66,10 @@ SIGNATURES = {
     "nd_out_residual_fwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "nd_qkv_pack_fwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "nd_qkv_pack_bwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "nd_gated_residual_fwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, *_SHAPE4, c_void_p]),
+    "nd_gated_residual_ws_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int64]),
+    "nd_gated_residual_bwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, *_SHAPE4, c_int64,
+                                      c_void_p]),
     "nd_fc1_fwd": (c_int, [c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float,
                            c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "nd_fc1_bwd_dz": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
@@ -173,6 +181,30 @@ def norm_fwd(kind, x, scale, shift, eps, *, stats=True, row_start=0, seq_len=Non
     return y, invstd
 
 
+def norm_fwd_e4m3(kind, x, scale, shift, eps, q_scale, amax=None, *, stats=True, row_start=0, seq_len=None):
+    """Forward with FP8 e4m3 output: returns (q, mean, invstd) / (q, inv_rms). `q_scale` is a device float (the
+    de-quantisation scale), `amax` an optional device float that receives max(amax, max |y|)."""
+    _need_cuda(x, scale, shift, q_scale, amax)
+    hidden = x.shape[-1]
+    if seq_len is None:
+        seq_len = x.shape[1] if x.dim() == 3 else 1
+    rows = x.numel() // hidden
+    q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    lead = x.shape[:-1]
+    dt = DTYPE_IDS[x.dtype]
+    invstd = torch.empty(lead, dtype=torch.float32, device=x.device) if stats else None
+    if kind == "layer":
+        mean = torch.empty(lead, dtype=torch.float32, device=x.device) if stats else None
+        check(lib().nd_adaln_fwd_e4m3(dt, _ptr(x), _ptr(scale), _ptr(shift), _ptr(q), _ptr(mean), _ptr(invstd),
+                                      _ptr(q_scale), _ptr(amax), rows, row_start, seq_len, hidden, eps, _stream()),
+              "nd_adaln_fwd_e4m3")
+        return q, mean, invstd
+    check(lib().nd_adarms_fwd_e4m3(dt, _ptr(x), _ptr(scale), _ptr(shift), _ptr(q), _ptr(invstd), _ptr(q_scale),
+                                   _ptr(amax), rows, row_start, seq_len, hidden, eps, _stream()),
+          "nd_adarms_fwd_e4m3")
+    return q, invstd
+
+
 def norm_bwd(kind, dy, x, scale, mean, invstd, *, mode="fused", row_start=0, seq_len=None, batch=None,
              dx=None, dscale=None, dshift=None, ws=None):
     """Backward. mode: "dx", "dparam" or "fused". Returns (dx, dscale, dshift) with None for parts
@@ -245,6 +277,40 @@ def gate_act_bwd(dy, x, act="silu", dz=None, gate_first=False):
     check(fn(DTYPE_IDS[x.dtype], ACT_IDS[act], _ptr(dy), _ptr(x), _ptr(dz), rows, inter, _stream()),
           "nd_gate_act_bwd_gate_first" if gate_first else "nd_gate_act_bwd")
     return dz
+
+
+# ---------------------------------------------------------------- gated residual
+GATED_TILE_ROWS = 8
+
+
+def gated_residual_fwd(x, branch, gate, *, row_start=0, seq_len=None):
+    """y = x + gate[b] * branch; x, branch [B,S,H] (or a row shard [rows,H] with row_start / seq_len), gate [B,H]."""
+    _need_cuda(x, branch, gate)
+    hidden = x.shape[-1]
+    if seq_len is None:
+        seq_len = x.shape[1] if x.dim() == 3 else 1
+    rows = x.numel() // hidden
+    y = torch.empty_like(x)
+    check(lib().nd_gated_residual_fwd(DTYPE_IDS[x.dtype], _ptr(x), _ptr(branch), _ptr(gate), _ptr(y), rows, row_start,
+                                      seq_len, hidden, _stream()), "nd_gated_residual_fwd")
+    return y
+
+
+def gated_residual_bwd(dy, branch, gate, *, row_start=0, seq_len=None):
+    """(dbranch, dgate_partials [samples, tiles, H] fp32); dgate = partials.sum(1)."""
+    _need_cuda(dy, branch, gate)
+    hidden = dy.shape[-1]
+    if seq_len is None:
+        seq_len = dy.shape[1] if dy.dim() == 3 else 1
+    rows = dy.numel() // hidden
+    L = lib()
+    nbytes = L.nd_gated_residual_ws_bytes(rows, row_start, seq_len, hidden, GATED_TILE_ROWS)
+    tiles = (seq_len + GATED_TILE_ROWS - 1) // GATED_TILE_ROWS
+    part = torch.empty(nbytes // (4 * hidden * tiles), tiles, hidden, dtype=torch.float32, device=dy.device)
+    dbranch = torch.empty_like(dy)
+    check(L.nd_gated_residual_bwd(DTYPE_IDS[dy.dtype], _ptr(dy), _ptr(branch), _ptr(gate), _ptr(dbranch), _ptr(part),
+                                  rows, row_start, seq_len, hidden, GATED_TILE_ROWS, _stream()), "nd_gated_residual_bwd")
+    return dbranch, part
 
 
 # ---------------------------------------------------------------- FC1

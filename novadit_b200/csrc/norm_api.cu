@@ -121,7 +121,8 @@ static int dispatch(int dtype, const NormArgs& a, void* stream) {
 
 static int norm_fwd(bool rms, int dtype, const void* x, const void* scale, const void* shift,
                     void* y, float* mean, float* invstd, int64_t rows, int64_t row_start,
-                    int64_t seq_len, int64_t hidden, float eps, void* stream) {
+                    int64_t seq_len, int64_t hidden, float eps, void* stream, const float* q_scale = nullptr,
+                    float* q_amax = nullptr) {
   if (int s = check_shape(rows, row_start, seq_len, hidden)) return s;
   if (rows == 0) return ND_OK;
   if (!x || !scale || !shift || !y) return ND_ERR_BAD_ARG;
@@ -133,6 +134,7 @@ static int norm_fwd(bool rms, int dtype, const void* x, const void* scale, const
   a.rows = rows; a.row_start = row_start;
   a.seq_len = static_cast<int>(seq_len); a.hidden = static_cast<int>(hidden);
   a.eps = eps; a.mode = kFwd; a.rms = rms;
+  a.q_scale = q_scale; a.q_amax = q_amax;
   return dispatch(dtype, a, stream);
 }
 
@@ -193,6 +195,25 @@ int nd_adaln_fwd(int dtype, const void* x, const void* scale, const void* shift,
                  int64_t hidden, float eps, void* stream) {
   return norm_fwd(false, dtype, x, scale, shift, y, mean, invstd, rows, row_start, seq_len, hidden,
                   eps, stream);
+}
+
+// Forward with FP8 e4m3 output for an FP8 consumer (FC1): q = saturate_e4m3(y / *q_scale) and, when `amax` is given,
+// *amax = max(*amax, max |y|) - the caller derives the next step's scale from it (delayed scaling) and zeroes it
+// when it wants a fresh maximum. Rows up to 192 16-byte vectors wide (H <= 1536 for 16-bit inputs).
+int nd_adaln_fwd_e4m3(int dtype, const void* x, const void* scale, const void* shift, void* q, float* mean,
+                      float* invstd, const float* q_scale, float* amax, int64_t rows, int64_t row_start,
+                      int64_t seq_len, int64_t hidden, float eps, void* stream) {
+  if (!q_scale) return ND_ERR_BAD_ARG;
+  return norm_fwd(false, dtype, x, scale, shift, q, mean, invstd, rows, row_start, seq_len, hidden, eps, stream,
+                  q_scale, amax);
+}
+
+int nd_adarms_fwd_e4m3(int dtype, const void* x, const void* scale, const void* shift, void* q, float* inv_rms,
+                       const float* q_scale, float* amax, int64_t rows, int64_t row_start, int64_t seq_len,
+                       int64_t hidden, float eps, void* stream) {
+  if (!q_scale) return ND_ERR_BAD_ARG;
+  return norm_fwd(true, dtype, x, scale, shift, q, nullptr, inv_rms, rows, row_start, seq_len, hidden, eps, stream,
+                  q_scale, amax);
 }
 
 int nd_adaln_bwd_dx(int dtype, const void* dy, const void* x, const void* scale,

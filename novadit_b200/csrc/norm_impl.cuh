@@ -49,6 +49,10 @@ struct NormArgs {
   int chunk_rem;         // rows % n_chunks
   int stages;    // shared-memory pipeline depth of the bulk-copy kernels
   int* err;    // device error word (set when a bounded wait expires)
+  // forward with e4m3 output (warp-per-row kernel only): y holds bytes, q = saturate_e4m3(value / *q_scale),
+  // *q_amax = max(*q_amax, max |value|) (nullable)
+  const float* q_scale;
+  float* q_amax;
 };
 
 // first row (local to the shard) of chunk c

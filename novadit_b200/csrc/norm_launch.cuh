@@ -57,20 +57,21 @@ inline long long resident_slots(const void* fn, int nt, int smem, bool fwd = tru
 }
 
 template <typename T, int VEC, int NV>
-static const void* pick_fwd_warp_nv(bool rms) {
+static const void* pick_fwd_warp_nv(bool rms, bool q8) {
+  if (q8) return rms ? (const void*)norm_fwd_warp<T, VEC, NV, true, true> : (const void*)norm_fwd_warp<T, VEC, NV, false, true>;
   return rms ? (const void*)norm_fwd_warp<T, VEC, NV, true> : (const void*)norm_fwd_warp<T, VEC, NV, false>;
 }
 
 // the warp-per-row forward kernel for rows of up to 6 x 32 vectors (H <= 1536 for 16-bit types); null beyond
 template <typename T, int VEC>
-static const void* pick_fwd_warp(int nvec, bool rms) {
+static const void* pick_fwd_warp(int nvec, bool rms, bool q8 = false) {
   switch ((nvec + 31) / 32) {
-    case 1: return pick_fwd_warp_nv<T, VEC, 1>(rms);
-    case 2: return pick_fwd_warp_nv<T, VEC, 2>(rms);
-    case 3: return pick_fwd_warp_nv<T, VEC, 3>(rms);
-    case 4: return pick_fwd_warp_nv<T, VEC, 4>(rms);
-    case 5: return pick_fwd_warp_nv<T, VEC, 5>(rms);
-    case 6: return pick_fwd_warp_nv<T, VEC, 6>(rms);
+    case 1: return pick_fwd_warp_nv<T, VEC, 1>(rms, q8);
+    case 2: return pick_fwd_warp_nv<T, VEC, 2>(rms, q8);
+    case 3: return pick_fwd_warp_nv<T, VEC, 3>(rms, q8);
+    case 4: return pick_fwd_warp_nv<T, VEC, 4>(rms, q8);
+    case 5: return pick_fwd_warp_nv<T, VEC, 5>(rms, q8);
+    case 6: return pick_fwd_warp_nv<T, VEC, 6>(rms, q8);
     default: return nullptr;
   }
 }
@@ -102,6 +103,10 @@ int launch_norm_fwd_warp(NormArgs a, const void* fn, cudaStream_t st) {
 
 template <typename T, int VEC>
 int launch_norm_tma(NormArgs a, cudaStream_t st) {
+  if (a.mode == kFwd && a.q_scale != nullptr) {  // e4m3 output exists in the warp-per-row kernel only
+    const void* fq = pick_fwd_warp<T, VEC>(a.hidden / VEC, a.rms, true);
+    return fq != nullptr ? launch_norm_fwd_warp<T, VEC>(a, fq, st) : ND_ERR_UNSUPPORTED;
+  }
   // forward of a large tensor (128 MB and up): one warp per row; measured faster there and slower below
   const bool large = static_cast<double>(a.rows) * a.hidden * sizeof(T) >= 128.0 * 1024 * 1024;
   if (a.mode == kFwd && (norm_variant() == 4 || (large && norm_variant() != 3))) {
@@ -189,8 +194,9 @@ int launch_norm(NormArgs a, cudaStream_t st) {
   const void* ptrs[] = {a.x, a.scale, a.shift, a.y, a.dy, a.dx, a.dscale, a.dshift, a.ws_part};
   for (const void* p : ptrs) vec_ok = vec_ok && aligned16(p);
   a.err = device_error_ptr();
-  if (!vec_ok) return launch_norm_generic<T, 1>(a, st);
-  if (a.hidden / VMAX <= 512 && norm_variant() != 1) return launch_norm_tma<T, VMAX>(a, st);
+  if (!vec_ok) return a.q_scale != nullptr ? ND_ERR_UNSUPPORTED : launch_norm_generic<T, 1>(a, st);
+  if (a.q_scale != nullptr && a.hidden / VMAX > 192) return ND_ERR_UNSUPPORTED;
+  if (a.q_scale != nullptr || (a.hidden / VMAX <= 512 && norm_variant() != 1)) return launch_norm_tma<T, VMAX>(a, st);
   return launch_norm_generic<T, VMAX>(a, st);
 }
 

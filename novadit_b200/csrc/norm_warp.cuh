@@ -20,6 +20,8 @@
 // step, one rounding on store. Every mbarrier wait is bounded (1 s).
 #pragma once
 
+#include <cuda_fp8.h>
+
 #include "norm_tma.cuh"
 
 namespace nd {
@@ -36,7 +38,11 @@ __host__ __device__ inline size_t norm_warp_smem(int hidden, int elem_bytes, int
 #ifndef ND_WARP_MINB
 #define ND_WARP_MINB 5
 #endif
-template <typename T, int VEC, int NV, bool RMS>
+// Q8: the output is FP8 e4m3 (one byte per element) under a caller-given scale, and the largest |value| of the
+// launch is folded into a device float with an atomic max - the delayed-scaling recipe: this step quantises with
+// the scale derived from an earlier step's maximum and records its own for the next one, so the activation
+// never exists in 16 bits and FC1's FP8 operand needs no separate amax / quantise pass.
+template <typename T, int VEC, int NV, bool RMS, bool Q8 = false>
 __global__ void __launch_bounds__(kWarpThreads, ND_WARP_MINB) norm_fwd_warp(const NormArgs a) {
   constexpr int NP = VEC / 2;   // float2 pairs per vector
   constexpr int NF4 = VEC / 4;  // float4 chunks per vector
@@ -82,6 +88,9 @@ __global__ void __launch_bounds__(kWarpThreads, ND_WARP_MINB) norm_fwd_warp(cons
       pc_valid = pc.next(a, RPI);
     }
   }
+
+  [[maybe_unused]] float q_inv = 1.f, q_max = 0.f;
+  if constexpr (Q8) q_inv = 1.f / __ldg(a.q_scale);
 
   int stage = 0;
   uint32_t parity = 0;          // phase of full[stage] to wait for
@@ -201,9 +210,25 @@ __global__ void __launch_bounds__(kWarpThreads, ND_WARP_MINB) norm_fwd_warp(cons
               out[2 * k] = __ffma2_rn(__fmul2_rn(X[p][2 * k], r2), make_float2(s4.x, s4.y), make_float2(h4.x, h4.y));
               out[2 * k + 1] = __ffma2_rn(__fmul2_rn(X[p][2 * k + 1], r2), make_float2(s4.z, s4.w), make_float2(h4.z, h4.w));
             }
-            Vec<T, VEC> o;
-            pack2<T, VEC>(out, o);
-            o.store(yrow + static_cast<long long>(v) * VEC);
+            if constexpr (Q8) {
+              unsigned short pk[NP];
+#pragma unroll
+              for (int i = 0; i < NP; ++i) {
+                q_max = fmaxf(q_max, fmaxf(fabsf(out[i].x), fabsf(out[i].y)));
+                pk[i] = __nv_cvt_float2_to_fp8x2(make_float2(out[i].x * q_inv, out[i].y * q_inv), __NV_SATFINITE, __NV_E4M3);
+              }
+              unsigned char* qrow = static_cast<unsigned char*>(a.y) + (r + warp) * static_cast<long long>(H);
+              if constexpr (VEC == 8) {
+                *reinterpret_cast<uint2*>(qrow + static_cast<long long>(v) * 8) =
+                    make_uint2(pk[0] | (static_cast<uint32_t>(pk[1]) << 16), pk[2] | (static_cast<uint32_t>(pk[3]) << 16));
+              } else {
+                *reinterpret_cast<uint32_t*>(qrow + static_cast<long long>(v) * 4) = pk[0] | (static_cast<uint32_t>(pk[1]) << 16);
+              }
+            } else {
+              Vec<T, VEC> o;
+              pack2<T, VEC>(out, o);
+              o.store(yrow + static_cast<long long>(v) * VEC);
+            }
           }
         }
       }
@@ -216,6 +241,14 @@ __global__ void __launch_bounds__(kWarpThreads, ND_WARP_MINB) norm_fwd_warp(cons
       }
       more = cc.next(a, RPI);
     } while (more && cc.b == b);
+  }
+  if constexpr (Q8) {
+    if (a.q_amax != nullptr) {
+#pragma unroll
+      for (int w = 16; w >= 1; w >>= 1) q_max = fmaxf(q_max, __shfl_xor_sync(0xffffffffu, q_max, w));
+      // non-negative floats order like their bit patterns: an integer max is a float max, and it is exact
+      if (lane == 0) atomicMax(reinterpret_cast<int*>(a.q_amax), __float_as_int(q_max));
+    }
   }
 }
 

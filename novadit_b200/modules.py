@@ -127,6 +127,7 @@ class AdaLNZeroBlock(nn.Module):
                  use_fused_fc1_bias_act: bool = True, activation: str = "gelu", zero_init: bool = True,
                  device=None, dtype=None) -> None:
         super().__init__()
+        self.use_fused = use_fused
         # `use_fused_fc1_bias_act` selects the MLP's function (gate = first half of fc1's output) for the fused and
         # the PyTorch stack alike; `use_fused` selects who evaluates it
         self.body = NovaDiTBlock(hidden_size, num_heads, mlp_ratio, use_fused_adaln=use_fused,
@@ -142,8 +143,9 @@ class AdaLNZeroBlock(nn.Module):
     def forward(self, x: torch.Tensor, cond: torch.Tensor) -> torch.Tensor:
         shift_a, scale_a, gate_a, shift_m, scale_m, gate_m = self.modulation(F.silu(cond)).chunk(6, dim=-1)
         body = self.body
-        x = x + gate_a.unsqueeze(1) * body.attn(body._adaln(x, scale_a.contiguous(), shift_a.contiguous()))
-        x = x + gate_m.unsqueeze(1) * body.mlp(body._adaln(x, scale_m.contiguous(), shift_m.contiguous()))
+        residual = ops.fused_gated_residual if self.use_fused else ops.gated_residual_ref
+        x = residual(x, body.attn(body._adaln(x, scale_a.contiguous(), shift_a.contiguous())), gate_a)
+        x = residual(x, body.mlp(body._adaln(x, scale_m.contiguous(), shift_m.contiguous())), gate_m)
         return x
 
 

@@ -41,6 +41,7 @@ from .adaln import (  # noqa: E402
     fused_adaln,
     fused_adaln_backward_dparam,
     fused_adaln_backward_dx,
+    fused_adaln_e4m3,
     fused_adaln_inference,
 )
 from .adarmsnorm import adarmsnorm_ref, fused_adarmsnorm, fused_adarmsnorm_inference  # noqa: E402
@@ -57,7 +58,12 @@ from .fc1_bias_act import (  # noqa: E402
 from .gate_act import fused_gate_act, fused_geglu, gate_act_ref, geglu_ref  # noqa: E402
 from .outside_path import adaln_compile, adarmsnorm_compile  # noqa: E402
 from .qkv_pack import fused_qkv_linear_pack, fused_qkv_pack, qkv_pack_ref  # noqa: E402
-from .residual import fused_out_residual, out_residual_ref  # noqa: E402
+from .residual import (  # noqa: E402
+    fused_gated_residual,
+    fused_out_residual,
+    gated_residual_ref,
+    out_residual_ref,
+)
 
 __all__ = [
     "HAS_NOVADIT_CUDA",
@@ -65,6 +71,7 @@ __all__ = [
     "adarmsnorm_ref",
     "adaln_ref",
     "fused_adaln",
+    "fused_adaln_e4m3",
     "fused_adaln_inference",
     "fused_adaln_backward_dparam",
     "fused_adaln_backward_dx",
@@ -82,7 +89,9 @@ __all__ = [
     "interleave_bias",
     "un_interleave_bias",
     "split_gated_weight",
+    "fused_gated_residual",
     "fused_out_residual",
+    "gated_residual_ref",
     "fused_qkv_linear_pack",
     "fused_qkv_pack",
     "adaln_compile",

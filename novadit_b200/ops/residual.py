@@ -35,3 +35,33 @@ def fused_out_residual(x, residual, bias=None):
     """x, residual [B,S,H] (CUDA, one dtype of fp32 / fp16 / bf16), bias [H] or None."""
     require_cuda_extension("fused_out_residual", x, "out_residual_ref")
     return _FusedOutResidualFunction.apply(x, residual, bias)
+
+
+def gated_residual_ref(x, branch, gate):
+    """y = x + gate[:, None, :] * branch (the adaLN-Zero residual of DiT blocks; not an operator of the reference)."""
+    return x + gate.unsqueeze(1) * branch
+
+
+class _FusedGatedResidualFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, branch, gate):
+        from .. import capi
+
+        require_cuda_extension("fused_gated_residual", x, "gated_residual_ref")
+        branch, gate = branch.contiguous(), gate.contiguous()
+        ctx.save_for_backward(branch, gate)
+        return capi.gated_residual_fwd(x.contiguous(), branch, gate)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .. import capi
+
+        branch, gate = ctx.saved_tensors
+        dbranch, part = capi.gated_residual_bwd(dy.contiguous(), branch, gate)
+        return dy, dbranch, part.sum(dim=1).to(gate.dtype)
+
+
+def fused_gated_residual(x, branch, gate):
+    """x, branch [B,S,H], gate [B,H] (CUDA, one dtype of fp32 / fp16 / bf16); differentiable in all three."""
+    require_cuda_extension("fused_gated_residual", x, "gated_residual_ref")
+    return _FusedGatedResidualFunction.apply(x, branch, gate)

@@ -73,3 +73,45 @@ def test_shape_errors_like_the_reference():
         ops.fused_qkv_pack(torch.zeros(2, 4, 50, device=DEV), 2, 8)
     with pytest.raises(RuntimeError):
         ops.fused_out_residual(torch.zeros(2, 4, 8), torch.zeros(2, 4, 8))  # CPU tensors: no fallback
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(2, 8, 16), (3, 77, 1152), (1, 1, 8), (2, 5, 770), (4, 256, 1152)])
+def test_gated_residual_forward_backward(dtype, shape):
+    gen = torch.Generator().manual_seed(5)
+    b, s, h = shape
+    x = torch.randn(shape, generator=gen).to(dtype)
+    br = torch.randn(shape, generator=gen).to(dtype)
+    gate = (torch.randn(b, h, generator=gen) * 0.5).to(dtype)
+    dy = torch.randn(shape, generator=gen).to(dtype)
+    xd, bd, gd = (t.to(DEV).requires_grad_(True) for t in (x, br, gate))
+    y = ops.fused_gated_residual(xd, bd, gd)
+    dx, dbr, dgate = torch.autograd.grad(y, (xd, bd, gd), dy.to(DEV))
+    x64, b64, g64 = (t.double().requires_grad_(True) for t in (x, br, gate))
+    want = ops.gated_residual_ref(x64, b64, g64)
+    wdx, wdbr, wdg = torch.autograd.grad(want, (x64, b64, g64), dy.double())
+    tol = 1e-6 if dtype == torch.float32 else HALF_REL_L2
+    assert rel_l2(y, want) < tol and rel_l2(dbr, wdbr) < tol and rel_l2(dgate, wdg) < tol
+    assert torch.equal(dx.cpu(), dy)
+    if dtype != torch.float32:  # one rounding of the fp32 result
+        half_ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+        err = (y.detach().cpu().double() - want.detach()).abs()
+        assert bool((err <= half_ulp * want.detach().abs() * 1.001 + 1e-7).all())
+
+
+def test_gated_residual_row_shard():
+    from novadit_b200 import capi
+
+    gen = torch.Generator().manual_seed(6)
+    b, s, h = 3, 50, 256
+    x, br, dy = (torch.randn(b, s, h, generator=gen).to(DEV, torch.bfloat16) for _ in range(3))
+    gate = torch.randn(b, h, generator=gen).to(DEV, torch.bfloat16)
+    full = capi.gated_residual_fwd(x, br, gate)
+    dbr_full, part_full = capi.gated_residual_bwd(dy, br, gate)
+    lo, hi = 37, 121
+    sl = lambda t: t.reshape(-1, h)[lo:hi].contiguous()  # noqa: E731
+    y = capi.gated_residual_fwd(sl(x), sl(br), gate, row_start=lo, seq_len=s)
+    dbr, part = capi.gated_residual_bwd(sl(dy), sl(br), gate, row_start=lo, seq_len=s)
+    assert torch.equal(y, sl(full)) and torch.equal(dbr, sl(dbr_full))
+    # the shard touches samples 0..2; the middle sample is complete inside it
+    assert torch.equal(part[1 - lo // s], part_full[1])
