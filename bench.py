@@ -274,6 +274,35 @@ def bench_extras(dev, stream, hbm_peak: float, tf_peak: float) -> dict:
     out["adaln_fwd_bwd_pytorch_eager_cuda"] = {"GB/s": STEP_BYTES / ms / 1e6, "ms_per_step": ms}
     del work
 
+    # the same kernels on 16 x the rows (B = 512: 131 072 rows, 302 MB per tensor, two buffer sets): where launch
+    # and first-byte latency stop mattering
+    big_b = 16 * B
+    xb = torch.randn(big_b, S, H, device=dev).to(torch.bfloat16)
+    gb = torch.randn(big_b, S, H, device=dev).to(torch.bfloat16)
+    sb = (torch.randn(big_b, H, device=dev) * 0.1).to(torch.bfloat16)
+    hb = (torch.randn(big_b, H, device=dev) * 0.1).to(torch.bfloat16)
+    big_sets = []
+    for _ in range(2):
+        big_sets.append({"x": xb.clone(), "dy": gb.clone(), "y": torch.empty_like(xb), "dx": torch.empty_like(xb),
+                         "mean": torch.empty(big_b, S, dtype=torch.float32, device=dev),
+                         "invstd": torch.empty(big_b, S, dtype=torch.float32, device=dev),
+                         "dscale": torch.empty(big_b, H, dtype=torch.float32, device=dev),
+                         "dshift": torch.empty(big_b, H, dtype=torch.float32, device=dev)})
+    del xb, gb
+
+    def big_step():
+        for st in big_sets:
+            capi.norm_fwd("layer", st["x"], sb, hb, EPS, y=st["y"], mean=st["mean"], invstd=st["invstd"])
+            capi.norm_bwd("layer", st["dy"], st["x"], sb, st["mean"], st["invstd"], dx=st["dx"], dscale=st["dscale"],
+                          dshift=st["dshift"])
+
+    big_step()
+    ms = time_graph_loop(capture(big_step), 5, stream) / 2
+    big_bytes = 16 * STEP_BYTES
+    out["adaln_fwd_bwd_131072_rows"] = {"GB/s": big_bytes / ms / 1e6, "ms_per_step": ms,
+                                        "frac_of_hbm_peak": big_bytes / ms / 1e6 / hbm_peak}
+    del big_sets
+
     # gate-act, workload config 3: x [8, 4096, 2*4608] bf16 (604 MB, far larger than L2)
     rows, inter = 8 * 4096, 4608
     x, dy = synth.gate_act_inputs(1, 2048, inter, torch.bfloat16, seed=3)

@@ -1,17 +1,23 @@
 // Fused FC1: y = epilogue((x @ w^T) * alpha + bias) on the 5th-generation tensor cores (sm_100a).
 //
 // One persistent CTA per SM, 320 threads, warp-specialised:
-//   warp 0      TMA producer: x and w tiles -> 128B-swizzled shared memory, 4-stage mbarrier ring
-//   warp 1      tcgen05.mma issuer (one lane) + owner of the tensor-memory allocation
+//   warp 0      TMA producer (one thread): x and w tiles -> 128B-swizzled shared memory, mbarrier ring
+//   warp 1      tcgen05.mma issuer (one thread) + owner of the tensor-memory allocation
 //   warps 2..9  epilogue (two warps per TMEM lane quarter, each taking half of the tile's columns):
-//               tcgen05.ld the fp32 accumulator, * alpha, + bias, activation
-//               (gated: value * act(gate)), round once, 64-byte row segments to global memory
+//               tcgen05.ld the fp32 accumulator, * alpha, + bias, activation (gated: value * act(gate)), round
+//               once, stage a 32 x 32 block in shared memory and hand it to the copy engine (bulk tensor store)
 // CTA tile: 128 rows x 256 accumulator columns x 128 bytes of K per stage. For the gated form
 // the 256 columns are 128 gate columns and the 128 value columns of the SAME output columns,
 // staged as one K-major B operand (gate rows then value rows), so a single UMMA of N=256
 // produces both halves and the epilogue combines TMEM columns c and 128+c. Two accumulators
-// (2 x 256 of the 512 TMEM columns) let the epilogue of tile i overlap the main loop of tile
-// i+1. No cluster: every CTA issues its own TMA loads.
+// (2 x 256 of the 512 TMEM columns) let the epilogue of tile i overlap the main loop of tile i+1.
+//
+// Three kernels share these pieces:
+//   fc1_kernel          single-CTA tiles (cta_group::1), 4 operand stages
+//   fc1_pair_kernel     two-CTA tiles (cta_group::2, clusters of two): 256 x 256 per pair, each CTA stages its A
+//                       rows and half of B, one MMA stream for both tensor cores; no multicast loads
+//   fc1_kernel<BWD>     the backward-dz variant: the same main loop (3 stages) with the activation BACKWARD as
+//                       epilogue - dy fetched by the copy engine, the two halves of dz stored as blocks
 //
 // Every wait on an mbarrier is bounded (1 s of %globaltimer); on expiry the waiting role raises
 // a CTA-wide abort flag, the status word in global memory is set, every role leaves its loop,
@@ -254,10 +260,9 @@ __device__ __forceinline__ void epilogue_columns(const Fc1Args& a, const CUtenso
 #pragma unroll
       for (int j4 = 0; j4 < 8; ++j4) {
         const float4 b = sb4[ch * 8 + j4];
-        out[4 * j4 + 0] = act_fwd<ACT>(fmaf(z[4 * j4 + 0], alpha, b.x));
-        out[4 * j4 + 1] = act_fwd<ACT>(fmaf(z[4 * j4 + 1], alpha, b.y));
-        out[4 * j4 + 2] = act_fwd<ACT>(fmaf(z[4 * j4 + 2], alpha, b.z));
-        out[4 * j4 + 3] = act_fwd<ACT>(fmaf(z[4 * j4 + 3], alpha, b.w));
+        // every accumulator gets an activation here: the special-function unit is the limit, so pairs share a reciprocal
+        act_fwd_pair<ACT>(fmaf(z[4 * j4 + 0], alpha, b.x), fmaf(z[4 * j4 + 1], alpha, b.y), out[4 * j4 + 0], out[4 * j4 + 1]);
+        act_fwd_pair<ACT>(fmaf(z[4 * j4 + 2], alpha, b.z), fmaf(z[4 * j4 + 3], alpha, b.w), out[4 * j4 + 2], out[4 * j4 + 3]);
       }
     }
     if (lane == 0) bulk_wait_read_all();  // the previous block has left the staging memory
