@@ -202,30 +202,6 @@ template <int ACT> __device__ __forceinline__ float act_fwd(float g) {
   }
 }
 
-// Two activations with ONE reciprocal: 1/a and 1/b from r = 1/(a b) as r b and r a. The special-function unit
-// (16 results per clock and SM) is what bounds an epilogue that applies an activation to every accumulator;
-// this trades a quarter of its work for three multiplies. The exponent arguments are clamped so that the product
-// of the two denominators stays finite (sigmoid below 2^-60 is returned as 2^-60: far below any output step).
-template <int ACT> __device__ __forceinline__ void act_fwd_pair(float g0, float g1, float& r0, float& r1) {
-  if constexpr (ACT == ND_ACT_NONE) {
-    r0 = g0;
-    r1 = g1;
-  } else {
-    float e0, e1;
-    if constexpr (ACT == ND_ACT_SILU) {
-      e0 = -1.4426950408889634f * g0;
-      e1 = -1.4426950408889634f * g1;
-    } else {
-      e0 = g0 * fmaf(kGeluE1, g0 * g0, kGeluE0);
-      e1 = g1 * fmaf(kGeluE1, g1 * g1, kGeluE0);
-    }
-    const float d0 = 1.f + ex2_approx(fminf(e0, 60.f)), d1 = 1.f + ex2_approx(fminf(e1, 60.f));
-    const float r = rcp_approx(d0 * d1);
-    r0 = g0 * (r * d1);
-    r1 = g1 * (r * d0);
-  }
-}
-
 // returns act(g) and writes act'(g)
 template <int ACT> __device__ __forceinline__ float act_fwd_grad(float g, float& grad) {
   if constexpr (ACT == ND_ACT_SILU) {

@@ -260,9 +260,10 @@ __device__ __forceinline__ void epilogue_columns(const Fc1Args& a, const CUtenso
 #pragma unroll
       for (int j4 = 0; j4 < 8; ++j4) {
         const float4 b = sb4[ch * 8 + j4];
-        // every accumulator gets an activation here: the special-function unit is the limit, so pairs share a reciprocal
-        act_fwd_pair<ACT>(fmaf(z[4 * j4 + 0], alpha, b.x), fmaf(z[4 * j4 + 1], alpha, b.y), out[4 * j4 + 0], out[4 * j4 + 1]);
-        act_fwd_pair<ACT>(fmaf(z[4 * j4 + 2], alpha, b.z), fmaf(z[4 * j4 + 3], alpha, b.w), out[4 * j4 + 2], out[4 * j4 + 3]);
+        out[4 * j4 + 0] = act_fwd<ACT>(fmaf(z[4 * j4 + 0], alpha, b.x));
+        out[4 * j4 + 1] = act_fwd<ACT>(fmaf(z[4 * j4 + 1], alpha, b.y));
+        out[4 * j4 + 2] = act_fwd<ACT>(fmaf(z[4 * j4 + 2], alpha, b.z));
+        out[4 * j4 + 3] = act_fwd<ACT>(fmaf(z[4 * j4 + 3], alpha, b.w));
       }
     }
     if (lane == 0) bulk_wait_read_all();  // the previous block has left the staging memory
