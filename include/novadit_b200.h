@@ -57,8 +57,8 @@ int nd_device_error(int reset);
 void nd_tune_norm_tile_rows(int tile_rows);
 /* Tuning hook: 0 = default (bulk-copy kernels where the row layout allows), 1 = generic kernels for
  * every shape, 3 / 4 = never / always run the forward pass with the warp-per-row kernel where it
- * applies (default: large tensors only). Results are identical up to fp32 summation order. No
- * counterpart in the reference. */
+ * applies (default: large tensors only), 5 = even row chunks instead of sample-aligned ones. Results
+ * are identical up to fp32 summation order. No counterpart in the reference. */
 void nd_tune_norm_variant(int variant);
 /* Tuning hook: pipeline depth (shared-memory stages) of the bulk-copy norm kernels; 0 = as many as
  * fit the per-CTA budget. No counterpart in the reference. */

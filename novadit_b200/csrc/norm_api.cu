@@ -62,7 +62,10 @@ __global__ void __launch_bounds__(128) norm_dparam_stage2_kernel(const NormArgs 
   const long long b = a.b_first + bi;
   const int H = a.hidden;
   long long first, count;
-  if (a.n_chunks > 0) {
+  if (a.n_chunks > 0 && a.chunks_per_sample > 0) {
+    first = bi * a.chunks_per_sample + bi;  // slot = chunk + sample index, chunks [bi k, (bi + 1) k)
+    count = a.chunks_per_sample;
+  } else if (a.n_chunks > 0) {
     long long s0 = b * a.seq_len - a.row_start, s1 = s0 + a.seq_len;  // the sample's rows, local, clipped below
     if (s0 < 0) s0 = 0;
     if (s1 > a.rows) s1 = a.rows;
@@ -175,8 +178,8 @@ extern "C" {
 void nd_tune_norm_tile_rows(int tile_rows) { g_tile_rows_override.store(tile_rows < 0 ? 0 : tile_rows); }
 
 // Tuning hook: 0 = default; 1 = the generic (register-fed) kernels even where the bulk-copy kernels apply;
-// 3 / 4 = never / always use the warp-per-row forward kernel where it applies (default: large tensors only).
-// Process-wide.
+// 3 / 4 = never / always use the warp-per-row forward kernel where it applies (default: large tensors only);
+// 5 = cut the rows evenly even where whole samples would allow sample-aligned chunks. Process-wide.
 void nd_tune_norm_variant(int variant) { g_norm_variant.store(variant); }
 // Tuning hook: shared-memory pipeline depth of the bulk-copy norm kernels (0 = as many as fit).
 void nd_tune_norm_stages(int stages) { g_norm_stages.store(stages < 0 ? 0 : stages); }

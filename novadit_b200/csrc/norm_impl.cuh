@@ -47,6 +47,8 @@ struct NormArgs {
   int n_chunks;  // bulk-copy kernels: the shard's rows are split evenly into this many chunks, one per CTA
   long long chunk_base;  // rows / n_chunks
   int chunk_rem;         // rows % n_chunks
+  int chunks_per_sample;  // > 0: the shard is whole samples and every sample is cut into this many chunks (no chunk
+                          // crosses a sample boundary); 0: the shard's rows are cut evenly, whatever the samples
   int stages;    // shared-memory pipeline depth of the bulk-copy kernels
   int* err;    // device error word (set when a bounded wait expires)
   // forward with e4m3 output (warp-per-row kernel only): y holds bytes, q = saturate_e4m3(value / *q_scale),

@@ -33,6 +33,16 @@ struct GroupCursor {
   long long r, r_end;   // next row, end of the chunk (local to the shard)
   long long b, s_end;   // sample of row r, end of that sample clipped to the chunk (local)
   __device__ __forceinline__ bool init(const NormArgs& a) {
+    if (a.chunks_per_sample > 0) {  // chunk j of sample bi: the sample's rows cut evenly
+      const long long k = a.chunks_per_sample;
+      const long long bi = blockIdx.x / k, j = blockIdx.x - bi * k;
+      const long long base = a.seq_len / k, rem = a.seq_len - base * k;
+      r = bi * a.seq_len + j * base + (j < rem ? j : rem);
+      r_end = r + base + (j < rem ? 1 : 0);
+      b = a.b_first + bi;
+      clip_sample(a);
+      return r < r_end;
+    }
     r = chunk_start(a.chunk_base, a.chunk_rem, blockIdx.x);
     r_end = chunk_start(a.chunk_base, a.chunk_rem, blockIdx.x + 1);
     if (r >= r_end) return false;
