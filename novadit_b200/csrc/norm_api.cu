@@ -86,19 +86,20 @@ __global__ void __launch_bounds__(128) norm_dparam_stage2_kernel(const NormArgs 
   const long long stride = 2LL * H;
   float acc = 0.f;
   long long t = 0;
-  for (; t + 8 <= count; t += 8) {  // eight independent loads in flight, summed in index order
-    float v[8];
+  constexpr int U = 16;  // independent loads in flight per round (a sample rarely has more partials than this)
+  for (; t + U <= count; t += U) {  // summed in index order
+    float v[U];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) v[u] = __ldcg(src + (t + u) * stride);
+    for (int u = 0; u < U; ++u) v[u] = __ldcg(src + (t + u) * stride);
 #pragma unroll
-    for (int u = 0; u < 8; ++u) acc += v[u];
+    for (int u = 0; u < U; ++u) acc += v[u];
   }
-  {
-    float v[8];
+  if (t < count) {
+    float v[U];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) v[u] = t + u < count ? __ldcg(src + (t + u) * stride) : 0.f;
+    for (int u = 0; u < U; ++u) v[u] = t + u < count ? __ldcg(src + (t + u) * stride) : 0.f;
 #pragma unroll
-    for (int u = 0; u < 8; ++u) acc += v[u];  // adding +0 keeps the order and the value
+    for (int u = 0; u < U; ++u) acc += v[u];  // adding +0 keeps the order and the value
   }
   float* dst = colx < H ? a.dscale + b * H + colx : a.dshift + b * H + (colx - H);
   *dst = acc;
