@@ -1,10 +1,11 @@
 // AdaLN / AdaRMSNorm kernels with a bulk-copy (TMA) pipeline into shared memory (sm_100a).
 //
-// Work split. The shard's rows are cut into `n_chunks` contiguous, equally sized chunks, one
-// per CTA and at most one CTA per resident slot, so a launch is a single balanced wave whatever
-// the batch and sequence sizes are. Inside its chunk a CTA walks groups of up to RPI rows that
-// never cross a sample boundary (the modulation vector and the dscale/dshift column sums are
-// per sample).
+// Work split. The shard's rows are cut into `n_chunks` contiguous chunks, one per CTA and at most
+// one CTA per resident slot, so a launch is a single wave whatever the batch and sequence sizes
+// are: `chunks_per_sample` equal chunks of every sample when the shard is whole samples and that
+// fills the slots (no chunk crosses a sample boundary then), equal chunks of the shard's rows
+// otherwise. Inside its chunk a CTA walks groups of up to RPI rows that never cross a sample
+// boundary (the modulation vector and the dscale/dshift column sums are per sample).
 //
 // Data path. The rows of a group are contiguous in global memory, so ONE cp.async.bulk per
 // input tensor lands a whole group in a shared-memory stage. Thread 0 keeps `stages` groups in
