@@ -52,23 +52,6 @@ int nd_version(void);
  * reset != 0 clears it. Negative = nd_status of a failed query. */
 int nd_device_error(int reset);
 
-/* Tuning hook: force the row-tile height of the generic norm kernels (0 = built-in choice).
- * Process-wide; affects nd_norm_dparam_ws_bytes. No counterpart in the reference. */
-void nd_tune_norm_tile_rows(int tile_rows);
-/* Tuning hook: 0 = default (bulk-copy kernels where the row layout allows), 1 = generic kernels for
- * every shape, 3 / 4 = never / always run the forward pass with the warp-per-row kernel where it
- * applies (default: large tensors only), 5 = even row chunks instead of sample-aligned ones. Results
- * are identical up to fp32 summation order. No counterpart in the reference. */
-void nd_tune_norm_variant(int variant);
-/* Tuning hook: pipeline depth (shared-memory stages) of the bulk-copy norm kernels; 0 = as many as
- * fit the per-CTA budget. No counterpart in the reference. */
-void nd_tune_norm_stages(int stages);
-/* Tuning hook: 0 launches the norm kernels without programmatic stream serialization (default 1:
- * each kernel may be scheduled while its predecessor in the stream drains). */
-void nd_tune_norm_pdl(int enabled);
-/* Tuning hook: cap on CTAs per SM of the bulk-copy norm kernels (0 = what occupancy allows). */
-void nd_tune_norm_chunks_per_sm(int n);
-
 /* ------------------------------------------------------------------ AdaLN */
 
 /* y = LN(x) * (1 + scale[b]) + shift[b]; writes fp32 mean / invstd per row when
@@ -255,19 +238,6 @@ int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const void* x, c
  * novadit/ops/fc1_bias_act.py:255-270. `status` as in nd_fc1_fwd. */
 int nd_fc1_bwd_dz(int dtype, int act, const void* x, const void* w, const void* bias, const void* dy,
                   void* dz, int64_t m, int64_t k, int64_t n, int* status, void* stream);
-
-/* Tuning hook for the gate-act kernels: rows per CTA group (1, 2 or 4; 0 = default) and 1 = a single
- * resident wave of CTAs striding over the groups instead of one CTA per group (default 0). Process-wide.
- * No counterpart in the reference. */
-void nd_tune_gate_act(int rows_per_group, int persistent);
-/* Tuning hook: 1 = two-CTA tiles (tcgen05 cta_group::2 over clusters of two CTAs), 0 = single-CTA
- * tiles, negative (default) = chosen per problem. Process-wide. No counterpart in the reference. */
-void nd_tune_fc1_pair(int mode);
-/* Diagnostic hook: a device array of 8 int64 that later nd_fc1_fwd launches add cycle counters to
- * ([0] copy thread waiting for a free stage, [3]/[4] one epilogue warp waiting / working, [5]/[7] the
- * copy thread's lifetime in cycles / nanoseconds); NULL (default) turns it off. No counterpart in the
- * reference. */
-void nd_tune_fc1_trace(long long* device_counters);
 
 /* amax = max |x| over n elements (fp32 result, device). Two-stage and deterministic:
  * `ws` holds per-CTA maxima; nd_amax_ws_bytes() bytes, 256-byte aligned. No counterpart in

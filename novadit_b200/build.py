@@ -67,6 +67,7 @@ def _hash_inputs(paths: list[str], extra: str) -> str:
 def _headers() -> list[str]:
     hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     hs.append(os.path.join(ROOT, "include", "novadit_b200.h"))
+    hs.append(os.path.join(ROOT, "include", "novadit_b200_tuning.h"))
     return hs
 
 

@@ -9,6 +9,7 @@
 #include <type_traits>
 
 #include "../../include/novadit_b200.h"
+#include "../../include/novadit_b200_tuning.h"
 
 namespace nd {
 

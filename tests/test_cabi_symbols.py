@@ -1,4 +1,4 @@
-"""The C-ABI library loads and exports every symbol `include/novadit_b200.h` declares (no GPU needed)."""
+"""The C-ABI library loads and exports every symbol the headers under `include/` declare (no GPU needed)."""
 from __future__ import annotations
 
 import ctypes
@@ -10,13 +10,20 @@ import pytest
 from novadit_b200 import capi
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-HEADER = os.path.join(ROOT, "include", "novadit_b200.h")
+HEADERS = [os.path.join(ROOT, "include", name) for name in ("novadit_b200.h", "novadit_b200_tuning.h")]
 
 
-def declared_symbols() -> list[str]:
-    text = open(HEADER).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(nd_[a-z0-9_]+)\s*\(", text)))
+def declared_symbols(headers=HEADERS) -> list[str]:
+    names = set()
+    for header in headers:
+        text = re.sub(r"/\*.*?\*/", "", open(header).read(), flags=re.S)
+        names.update(re.findall(r"\b(nd_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
+
+
+def test_operator_header_holds_no_tuning_hook():
+    assert not [n for n in declared_symbols(HEADERS[:1]) if n.startswith("nd_tune_")]
+    assert all(n.startswith("nd_tune_") for n in declared_symbols(HEADERS[1:]))
 
 
 def test_header_declares_the_expected_entry_points():
