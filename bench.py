@@ -50,10 +50,19 @@ ROWS = B * S
 FWD_BYTES = 2 * ROWS * H * E + 2 * B * H * E + 2 * ROWS * 4                       # 37 961 728
 BWD_BYTES = 3 * ROWS * H * E + B * H * E + 2 * ROWS * 4 + 2 * B * H * 4           # 57 057 280
 STEP_BYTES = FWD_BYTES + BWD_BYTES                                                # 95 019 008
-# DRAM traffic per launch of the dominant kernel measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum
-# of norm_bwd_tma at this shape, profiles/norm_config2_adaln.md): 37 915 392 B read + 258 560 B written. The
-# 18.9 MB of dx is still dirty in L2 when the kernel ends, hence traffic < algorithmic bytes.
-NCU_TRAFFIC_BWD = 38173952
+WORKLOAD = "config2: AdaLN fwd+bwd, x [32,256,1152] bf16, eps 1e-6"   # the same string in both arms
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "norm_config2_traffic.json")
+
+
+def measured_traffic() -> tuple[int | None, dict | None]:
+    """DRAM bytes per launch of the dominant kernel from the tracked ncu record (read + written), and the record
+    itself (it names the capture's command and the commit it was taken at). None when the file is absent."""
+    try:
+        with open(TRAFFIC_FILE) as f:
+            rec = json.load(f)
+        return int(rec["dram_bytes_read"]) + int(rec["dram_bytes_write"]), rec
+    except Exception:
+        return None, None
 
 
 def measured_peaks() -> tuple[float, float, str]:
@@ -65,6 +74,15 @@ def measured_peaks() -> tuple[float, float, str]:
         return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
     except Exception:
         return 6650.0, 1590.0, "fallback"
+
+
+def measured_sustained_tflops(burst: float) -> float:
+    """bf16 TFLOP/s of a seconds-long cuBLAS loop under the power cap (MEASURED_PEAKS.json), else 0.88 x burst."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops_sustained"])
+    except Exception:
+        return 0.88 * burst
 
 
 class ClockSampler:
@@ -156,7 +174,7 @@ def run_reference_arm(args) -> None:
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": ran, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "config2: AdaLN fwd+bwd, x [32,256,1152] bf16, eps 1e-6", "where": "host CPU"},
+        "config": {"workload": WORKLOAD}, "setup": {"where": "host CPU"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -189,6 +207,27 @@ def replay_steps(big, singles, k: int) -> None:
         big.replay()
     for i in range(k % NSETS):
         singles[i].replay()
+
+
+GRAPH_STEPS = 256  # steps per graph of the timed region (a whole number of rotations)
+
+
+class StepGraphs:
+    """Graphs that replay EXACTLY k steps with no single-step launches: k // 256 replays of a 256-step graph and
+    one graph holding the remaining k % 256 steps (graph launches cost the host ~10 us each, which shows when a
+    graph holds one 27 us step)."""
+
+    def __init__(self, work: "NormWorkload", k: int) -> None:
+        self.whole = k // GRAPH_STEPS
+        rest = k % GRAPH_STEPS
+        self.big = capture(lambda: [work.step(work.sets[i % NSETS]) for i in range(GRAPH_STEPS)]) if self.whole else None
+        self.rest = capture(lambda: [work.step(work.sets[i % NSETS]) for i in range(rest)]) if rest else None
+
+    def replay(self) -> None:
+        for _ in range(self.whole):
+            self.big.replay()
+        if self.rest is not None:
+            self.rest.replay()
 
 
 class NormWorkload:
@@ -242,7 +281,7 @@ def time_graph_loop(graph, reps: int, stream) -> float:
     return event_time_ms(lambda: [graph.replay() for _ in range(reps)], stream) / reps
 
 
-def bench_extras(dev, stream, hbm_peak: float, tf_peak: float) -> dict:
+def bench_extras(dev, stream, hbm_peak: float, tf_peak: float, tf_sustained: float) -> dict:
     """The other operators of the path, each timed alone (cold inputs by rotation or size > L2)."""
     from novadit_b200 import capi, synth
 
@@ -371,8 +410,172 @@ def bench_extras(dev, stream, hbm_peak: float, tf_peak: float) -> dict:
                                   "frac_of_nominal_4500": flops / ms / 1e9 / 4500.0}
     g = capture(lambda: capi.quantize_e4m3(xf))
     out["fp8_quantise_x_ms"] = time_graph_loop(g, 20, stream)
+    del xf, wf, bf, qx, qw, y
+
+    # FC1, the large case of workload config 4: M=32768, K=3072, N=12288 (2.47 TFLOP per launch, ~2 ms: a kernel
+    # this long runs under the power cap, so its fraction is taken of the SUSTAINED bf16 figure)
+    m, k, n = 32768, 3072, 12288
+    flops = 2.0 * m * k * n
+    xl = torch.randn(m, k, device=dev).to(torch.bfloat16)
+    wl = (torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16)
+    bl = (torch.randn(n, device=dev) * 0.02).to(torch.bfloat16)
+    qxl, sxl = capi.quantize_e4m3(xl)
+    qwl, swl = capi.quantize_e4m3(wl)
+    scales_l = torch.cat([sxl, swl])
+    for name, gated in (("gated", 1), ("plain", 0)):
+        yl = torch.empty(m, n // 2 if gated else n, dtype=torch.bfloat16, device=dev)
+        capi.fc1_fwd(xl, wl, bl, "gelu", gated, y=yl, status=status)
+        ms = time_graph_loop(capture(lambda: capi.fc1_fwd(xl, wl, bl, "gelu", gated, y=yl, status=status)), 10, stream)
+        out[f"fc1_large_bf16_{name}"] = {"TFLOP/s": flops / ms / 1e9, "ms": ms,
+                                         "frac_of_bf16_sustained": flops / ms / 1e9 / tf_sustained,
+                                         "frac_of_bf16_peak": flops / ms / 1e9 / tf_peak}
+        capi.fc1_fwd(qxl, qwl, bl, "gelu", gated, alpha_dev=scales_l, out_dtype=torch.bfloat16, y=yl, status=status)
+        ms = time_graph_loop(capture(lambda: capi.fc1_fwd(qxl, qwl, bl, "gelu", gated, alpha_dev=scales_l,
+                                                          out_dtype=torch.bfloat16, y=yl, status=status)), 10, stream)
+        out[f"fc1_large_fp8_{name}"] = {"TFLOP/s": flops / ms / 1e9, "ms": ms,
+                                        "frac_of_measured_fp8_peak": flops / ms / 1e9 / fp8_peak if fp8_peak else None,
+                                        "frac_of_2x_bf16_sustained": flops / ms / 1e9 / (2 * tf_sustained)}
+        del yl
+    ms = time_graph_loop(capture(lambda: F.linear(xl, wl, bl)), 10, stream)
+    out["fc1_large_bf16_gemm_only_cublaslt"] = {"TFLOP/s": flops / ms / 1e9, "ms": ms}
     out["fc1_status_word"] = int(status.item())
     return out
+
+
+def bench_sharded(dev, stream, rank: int, world: int, hbm_peak: float, tf_peak: float) -> dict | None:
+    """The multi-GPU cases of the path, run by EVERY rank and reduced to rank 0 (max of the per-rank device times):
+    (i) strong scaling of the fixed config-2 tensor (8192 rows / N per rank, whole samples, no collective),
+    (ii) a tensor whose samples span ranks (B = 2, S = 4096; B = 1, S = 8192 on two ranks), where the packed
+    fp32 dscale/dshift go through ONE NCCL all-reduce - checked against the unsharded result and for bitwise
+    reproducibility, (iii) FC1 of config 4 with the weights replicated, rows per rank (weak) and rows sharded
+    (strong). With one rank (i) and (iii) are the one-GPU numbers and (ii) runs without a collective."""
+    import torch.distributed as dist
+
+    from novadit_b200 import capi, shard as sh, synth
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def all_true(flag: bool) -> bool:
+        if world == 1:
+            return flag
+        t = torch.tensor([1 if flag else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    out = {}
+    # (i) strong scaling: this rank's block of the ONE config-2 tensor; enough rotating sets that inputs stay cold
+    x, scale, shift, dy = synth.norm_inputs(B, S, H, torch.bfloat16, seed=0)
+    s = sh.make_shard(ROWS, S, world, rank)
+    xs, gs = x.reshape(-1, H)[s.start:s.end], dy.reshape(-1, H)[s.start:s.end]
+    sd, hd = scale.to(dev), shift.to(dev)
+    nsets = NSETS * world
+    sets = []
+    for i in range(nsets):
+        xi = torch.roll(xs, i, 0).to(dev).contiguous()
+        sets.append({"x": xi, "dy": torch.roll(gs, i, 0).to(dev).contiguous(), "y": torch.empty_like(xi),
+                     "dx": torch.empty_like(xi), "mean": torch.empty(s.count, dtype=torch.float32, device=dev),
+                     "invstd": torch.empty(s.count, dtype=torch.float32, device=dev),
+                     "dscale": torch.zeros(B, H, dtype=torch.float32, device=dev),
+                     "dshift": torch.zeros(B, H, dtype=torch.float32, device=dev)})
+
+    def shard_step(st):
+        capi.norm_fwd("layer", st["x"], sd, hd, EPS, y=st["y"], mean=st["mean"], invstd=st["invstd"],
+                      row_start=s.start, seq_len=S)
+        capi.norm_bwd("layer", st["dy"], st["x"], sd, st["mean"], st["invstd"], dx=st["dx"], dscale=st["dscale"],
+                      dshift=st["dshift"], row_start=s.start, seq_len=S, batch=B)
+
+    shard_step(sets[0])
+    torch.cuda.synchronize()
+    g = capture(lambda: [shard_step(st) for st in sets])
+    if world > 1:
+        dist.barrier()
+    ms = max_over_ranks(statistics.median(time_graph_loop(g, 10, stream) for _ in range(5)) / nsets)
+    out["adaln_config2_strong"] = {"rows_per_gpu": s.count, "ms_per_step": ms, "GB/s": STEP_BYTES / ms / 1e6,
+                                   "frac_of_n_x_hbm_peak": STEP_BYTES / ms / 1e6 / (world * hbm_peak),
+                                   "collective": "none (whole samples per GPU)"}
+    del sets, g
+
+    # (ii) samples that span ranks: the all-reduce carries data
+    b2, s2 = (2, 4096) if world != 2 else (1, 8192)
+    x, scale, shift, dy = synth.norm_inputs(b2, s2, H, torch.bfloat16, seed=5)
+    rows2 = b2 * s2
+    s = sh.make_shard(rows2, s2, world, rank)
+    xs = x.reshape(-1, H)[s.start:s.end].to(dev).contiguous()
+    gs = dy.reshape(-1, H)[s.start:s.end].to(dev).contiguous()
+    sd, hd = scale.to(dev), shift.to(dev)
+    _, mean, invstd = capi.norm_fwd("layer", xs, sd, hd, EPS, row_start=s.start, seq_len=s2)
+    runs = []
+    for _ in range(2):
+        dx, ds, dh = sh.norm_backward_sharded("layer", gs, xs, sd, mean, invstd, s, b2)
+        torch.cuda.synchronize()
+        runs.append((dx.clone(), ds.clone(), dh.clone()))
+    reproducible = all_true(all(torch.equal(p, q) for p, q in zip(*runs)))
+    # the unsharded result of one GPU (every rank computes it: the tensor is 19 MB)
+    xf, gf = x.reshape(-1, H).to(dev), dy.reshape(-1, H).to(dev)
+    _, mf, rf = capi.norm_fwd("layer", xf, sd, hd, EPS, seq_len=s2)
+    wdx, wds, wdh = capi.norm_bwd("layer", gf, xf, sd, mf, rf, seq_len=s2, batch=b2)
+
+    def rel_l2(a, b):
+        return float((a.double() - b.double()).norm() / b.double().norm().clamp_min(1e-30))
+
+    mine = list(s.samples())
+    errs = [rel_l2(runs[0][1][mine], wds[mine]), rel_l2(runs[0][2][mine], wdh[mine])]
+    err = max_over_ranks(max(errs))
+    dx_equal = all_true(torch.equal(runs[0][0], wdx[s.start:s.end]))
+    if err > 1e-4 or not reproducible:
+        raise AssertionError(f"sharded backward: rel-L2 {err:.3e} (bar 1e-4), reproducible {reproducible}")
+    reps = 20
+
+    def sharded_steps():
+        for _ in range(reps):
+            capi.norm_fwd("layer", xs, sd, hd, EPS, mean=mean, invstd=invstd, row_start=s.start, seq_len=s2)
+            sh.norm_backward_sharded("layer", gs, xs, sd, mean, invstd, s, b2)
+
+    sharded_steps()
+    if world > 1:
+        dist.barrier()
+    ms = max_over_ranks(statistics.median(event_time_ms(sharded_steps, stream) for _ in range(5)) / reps)
+    packed = torch.zeros(2, b2, H, dtype=torch.float32, device=dev)
+    ar_ms = 0.0
+    if world > 1:
+        def reduces():
+            for _ in range(reps):
+                dist.all_reduce(packed)
+        reduces()
+        dist.barrier()
+        ar_ms = max_over_ranks(statistics.median(event_time_ms(reduces, stream) for _ in range(5)) / reps)
+    step_bytes2 = 5 * rows2 * H * E
+    out["adaln_straddling"] = {"shape": [b2, s2, H], "rows_per_gpu": s.count,
+                               "collective": "NCCL all_reduce of [2,B,H] fp32" if sh.needs_allreduce(rows2, s2, world) else "none",
+                               "ms_per_step": ms, "GB/s": step_bytes2 / ms / 1e6, "allreduce_alone_ms": ar_ms,
+                               "allreduce_bytes": packed.numel() * 4, "dparam_rel_l2_vs_unsharded": err,
+                               "dx_bitwise_equal_unsharded": dx_equal, "bitwise_reproducible": reproducible,
+                               "launch": "eager (20 steps per sample, median of 5)"}
+    del xf, gf, wdx, runs
+
+    # (iii) FC1 of config 4, weights replicated
+    m, k, n = 8192, 1152, 4608
+    xc, wc, bc = (t.to(dev) for t in synth.fc1_inputs(m, k, n, torch.bfloat16, seed=0))
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    for name, rows_here in (("weak", m), ("strong", m // world)):
+        xr = xc[:rows_here].contiguous()
+        yr = torch.empty(rows_here, n // 2, dtype=torch.bfloat16, device=dev)
+        capi.fc1_fwd(xr, wc, bc, "gelu", 1, y=yr, status=status)
+        g = capture(lambda: capi.fc1_fwd(xr, wc, bc, "gelu", 1, y=yr, status=status))
+        if world > 1:
+            dist.barrier()
+        ms = max_over_ranks(statistics.median(time_graph_loop(g, 50, stream) for _ in range(3)))
+        total = 2.0 * rows_here * k * n * world
+        out[f"fc1_bf16_gated_{name}"] = {"rows_per_gpu": rows_here, "ms": ms, "TFLOP/s_all_gpus": total / ms / 1e9,
+                                         "frac_of_n_x_bf16_peak": total / ms / 1e9 / (world * tf_peak)}
+        del g
+    out["fc1_status_word"] = int(status.item())
+    return out if rank == 0 else None
 
 
 def bench_e2e(dev, k: int) -> dict:
@@ -418,6 +621,7 @@ def run_gpu_arm(args) -> None:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     hbm_peak, tf_peak, peak_src = measured_peaks()
+    tf_sustained = measured_sustained_tflops(tf_peak)
     steps, warmup = max(1, args.steps), max(3, args.warmup)
     stream = torch.cuda.current_stream()
 
@@ -441,14 +645,24 @@ def run_gpu_arm(args) -> None:
             big.replay()
         torch.cuda.synchronize()
 
-    # Timed region: exactly `steps` steps.
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    replay_steps(big, singles, steps)
-    e1.record(stream)
-    barrier()
-    elapsed_ms = e0.elapsed_time(e1)
+    # Timed region: exactly `steps` steps between two events, barrier + synchronize on both sides. One untimed
+    # rotation is queued right before the first event so that the first timed step does not start on an idle GPU,
+    # and the region is repeated: the per-rank median is reported (then the maximum over ranks).
+    est_s = steps * 30e-6
+    repeats = 25 if est_s * 25 <= 5.0 else max(3, int(5.0 / est_s))
+    timed = StepGraphs(work, steps)
+    timed.replay()  # first launch of the new graphs, untimed
+    samples_ms = []
+    for _ in range(repeats):
+        barrier()
+        big.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        timed.replay()
+        e1.record(stream)
+        barrier()
+        samples_ms.append(e0.elapsed_time(e1))
+    elapsed_ms = statistics.median(samples_ms)
 
     # Per-kernel durations for the roofline (same buffers, same rotation), still under the sampler.
     reps = max(4, min(200, steps // NSETS + 1))
@@ -472,10 +686,14 @@ def run_gpu_arm(args) -> None:
     e2e_line = {"value": world * STEP_BYTES / e2e_sec / 1e9, "unit": UNIT, **e2e}
 
     extras, cpu_line = None, None
+    multi = None
+    if not args.no_extras:
+        multi = bench_sharded(dev, stream, rank, world, hbm_peak, tf_peak)  # every rank takes part
     if rank == 0 and not args.no_extras:
-        extras = bench_extras(dev, stream, hbm_peak, tf_peak)
+        extras = bench_extras(dev, stream, hbm_peak, tf_peak, tf_sustained)
         extras["adaln_fwd_kernel"] = {"ms": fwd_ms, "GB/s": FWD_BYTES / fwd_ms / 1e6,
                                       "frac_of_hbm_peak": FWD_BYTES / fwd_ms / 1e6 / hbm_peak}
+        extras["sharded"] = multi
     if rank == 0 and world == 1 and not args.no_cpu:
         sec, ran, threads = cpu_reference_step_time(200, 1, budget_s=10.0)
         cpu_line = {"value": STEP_BYTES / sec / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
@@ -484,18 +702,28 @@ def run_gpu_arm(args) -> None:
 
     if rank == 0:
         achieved = BWD_BYTES / bwd_ms / 1e6
+        traffic, traffic_rec = measured_traffic()
+        fc1 = (extras or {}).get("fc1_bf16_gated")
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "config2: AdaLN fwd+bwd, x [32,256,1152] bf16, eps 1e-6, per GPU",
-                       "global_rows": world * ROWS, "parallelism": f"rows sharded over {world} GPU(s), no collective",
-                       "cold_cache": f"{NSETS} rotating buffer sets (605 MB > 4x L2)", "launch": "CUDA graphs"},
+            "config": {"workload": WORKLOAD},
+            "setup": {"per_gpu": "one config-2 batch per GPU", "global_rows": world * ROWS,
+                      "parallelism": f"rows sharded over {world} GPU(s), no collective",
+                      "cold_cache": f"{NSETS} rotating buffer sets (605 MB > 4x L2)", "launch": "CUDA graphs",
+                      "repeats": repeats, "timed": "median over repeats of the exact `steps`-step region, max over ranks",
+                      "ms_per_step_min_max": [min(samples_ms) / steps, max(samples_ms) / steps]},
+            "repeats": repeats,
             "frac_of_hbm_peak": value / world / hbm_peak,
             "roofline": {"kernel": "norm_bwd_tma + norm_dparam_stage2 (dx + dscale/dshift, one pass over dy and x)", "bound": "hbm",
                          "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                         "traffic": NCU_TRAFFIC_BWD, "peak_source": peak_src, "algorithmic_bytes": BWD_BYTES,
-                         "avg_launch_ms": bwd_ms},
+                         "traffic": traffic, "traffic_record": traffic_rec, "peak_source": peak_src,
+                         "algorithmic_bytes": BWD_BYTES, "avg_launch_ms": bwd_ms},
+            "roofline_fc1": None if not fc1 else {
+                "kernel": "fc1_pair_kernel (tcgen05, gated GELU-tanh epilogue), config 4 bf16", "bound": "tensor",
+                "achieved": fc1["TFLOP/s"], "peak": tf_peak, "unit": "TFLOP/s", "frac": fc1["TFLOP/s"] / tf_peak,
+                "flops": 2.0 * 8192 * 1152 * 4608, "avg_launch_ms": fc1["ms"], "peak_source": peak_src + " (burst)"},
             "e2e": e2e_line, "gpu_launches": 3 * steps, "clocks": clocks,
             "cpu_baseline": cpu_line, "extras": extras,
         }

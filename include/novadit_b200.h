@@ -48,7 +48,10 @@ const char* nd_status_string(int status);
 int nd_last_cuda_error(void);
 int nd_version(void);
 /* Error word of the current device: 0, or the code a kernel left when one of its bounded waits
- * (on a bulk copy into shared memory) expired. Synchronises with the device (a blocking copy).
+ * expired (1..3: a norm kernel waiting for a bulk copy into shared memory; 101..114: an FC1 kernel
+ * waiting for an operand stage, an accumulator or a dy block - its output is then incomplete).
+ * Covers every kernel of the library, including launches made through the torch extension, which
+ * passes no status word of its own. Synchronises with the device (a blocking copy).
  * reset != 0 clears it. Negative = nd_status of a failed query. */
 int nd_device_error(int reset);
 
@@ -118,7 +121,10 @@ int nd_adaln_bwd(int dtype, const void* dy, const void* x, const void* scale, co
  * The call allocates nothing and calls no allocating routine. Problems whose
  * nd_norm_dparam_ws_bytes(...) exceeds the array are refused with ND_ERR_TOO_LARGE (use nd_adaln_bwd
  * with your own workspace). The first call on each device looks up the array's device address
- * (cudaGetSymbolAddress, with that device current) and should come before any stream capture. All
+ * (cudaGetSymbolAddress, with that device current) and should come before any stream capture. It is
+ * also the call that makes the CUDA runtime load the array and the kernels onto that device (modules load
+ * lazily): a process that later hands all free device memory to its own pool should make one small
+ * warm-up call per device at start-up, before it does so, or that first call fails with ND_ERR_LAUNCH. All
  * calls on a device share the one array: calls whose kernels may overlap on the GPU (different
  * streams) race on it and must be serialised by the caller. The array keeps the previous call's
  * contents; nothing in it needs clearing. Same arguments and results as nd_adaln_bwd. */

@@ -124,9 +124,22 @@ def _stream() -> int:
 
 
 def _need_cuda(*ts: torch.Tensor) -> None:
+    """Every tensor contiguous, on CUDA, on ONE device, and that device current: the C ABI launches on the current
+    device's stream, so pointers of another device would be handed to the wrong GPU (the torch extension sets
+    the device itself; this ctypes layer asks the caller to)."""
+    dev = None
     for t in ts:
-        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+        if t is None:
+            continue
+        if not t.is_cuda or not t.is_contiguous():
             raise NovaditError("tensors must be contiguous CUDA tensors")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise NovaditError(f"tensors on different devices: {dev} and {t.device}")
+    if dev is not None and dev.index != torch.cuda.current_device():
+        raise NovaditError(f"tensors live on {dev} but the current device is cuda:{torch.cuda.current_device()}: "
+                           f"wrap the call in `with torch.cuda.device({dev.index})`")
 
 
 class Workspace:
@@ -352,13 +365,14 @@ def quantize_e4m3(x):
     _need_cuda(x)
     L = lib()
     dev = x.device
-    ws = _AMAX_WS.get(dev)
+    st = _stream()
+    key = (dev, st or 0)  # per device AND stream: two streams must not share the per-CTA maxima
+    ws = _AMAX_WS.get(key)
     if ws is None:
-        ws = _AMAX_WS[dev] = torch.empty(L.nd_amax_ws_bytes(), dtype=torch.uint8, device=dev)
+        ws = _AMAX_WS[key] = torch.empty(L.nd_amax_ws_bytes(), dtype=torch.uint8, device=dev)
     amax = torch.empty(1, dtype=torch.float32, device=dev)
     scale = torch.empty(1, dtype=torch.float32, device=dev)
     q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=dev)
-    st = _stream()
     check(L.nd_amax(DTYPE_IDS[x.dtype], _ptr(x), x.numel(), _ptr(amax), _ptr(ws), ws.numel(), st), "nd_amax")
     check(L.nd_quant_e4m3(DTYPE_IDS[x.dtype], _ptr(x), x.numel(), _ptr(amax), _ptr(q), _ptr(scale), st),
           "nd_quant_e4m3")

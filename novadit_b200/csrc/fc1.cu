@@ -20,7 +20,7 @@
 //                       epilogue - dy fetched by the copy engine, the two halves of dz stored as blocks
 //
 // Every wait on an mbarrier is bounded (1 s of %globaltimer); on expiry the waiting role raises
-// a CTA-wide abort flag, the status word in global memory is set, every role leaves its loop,
+// a CTA-wide abort flag, the caller's status word and the device error word are set, every role leaves its loop,
 // the producer lets its copies in flight land, and tensor memory is freed before the CTA exits.
 #include <cuda.h>
 #include <cuda_fp8.h>
@@ -47,11 +47,18 @@ constexpr int kOutBlockBytes = 32 * 32 * 2;  // 32 rows x 32 output columns of a
 constexpr int kGroupM = 8;       // tile rasterisation: m-blocks per group
 constexpr unsigned long long kWaitLimitNs = 1000000000ull;
 
+// Where an expired wait is recorded: the caller's status word (nullable) and the device error word that
+// nd_device_error() reads (codes 101.. there, so that they cannot be mistaken for the norm kernels' 1..3).
+struct Fc1Sink {
+  int* status;
+  int* err;
+};
+
 struct Fc1Args {
   const void* bias;        // out dtype, length n (nullable)
   void* y;
   const float* alpha_dev;  // nullable, two floats multiplied into alpha
-  int* status;             // nullable
+  Fc1Sink sink;
   long long* trace;        // nullable: per-role cycle counters (see nd_tune_fc1_trace)
   float alpha_host;
   int m, k, n;             // n = rows of w
@@ -80,7 +87,7 @@ using Fc1BwdSmem = Fc1SmemT<kBwdStages, 3>;
 
 // Bounded wait. Returns false if the CTA is aborting or the limit expired (and raises the abort).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+                                          Fc1Sink sink, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   for (uint32_t polls = 1;; ++polls) {
@@ -89,7 +96,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       if (*abort_flag) return false;
       if (global_ns() - t0 > kWaitLimitNs) {
         *abort_flag = 1;
-        if (status != nullptr) atomicCAS(status, 0, code);
+        if (sink.status != nullptr) atomicCAS(sink.status, 0, code);
+        if (sink.err != nullptr) atomicCAS(sink.err, 0, 100 + code);
         return false;
       }
     }
@@ -97,11 +105,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // mbar_wait that also adds the cycles spent waiting to a per-role counter (lane 0 only; `acc` may be null)
-__device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+__device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity, volatile int* abort_flag, Fc1Sink sink,
                                                 int code, long long* acc) {
-  if (acc == nullptr) return mbar_wait(bar, parity, abort_flag, status, code);
+  if (acc == nullptr) return mbar_wait(bar, parity, abort_flag, sink, code);
   const long long t0 = clock64();
-  const bool ok = mbar_wait(bar, parity, abort_flag, status, code);
+  const bool ok = mbar_wait(bar, parity, abort_flag, sink, code);
   *acc += clock64() - t0;
   return ok;
 }
@@ -318,7 +326,7 @@ __device__ __forceinline__ void epilogue_columns_bwd(const Fc1Args& a, const CUt
     tc_ld32(t_lane + ch * 32, g);
     tc_ld32(t_lane + 128 + ch * 32, v);
     tc_wait_ld();
-    ok = __all_sync(0xffffffffu, mbar_wait(dy_bar, dy_phase, abort_flag, a.status, 5));
+    ok = __all_sync(0xffffffffu, mbar_wait(dy_bar, dy_phase, abort_flag, a.sink, 5));
     if (!ok) return;
     dy_phase ^= 1u;
     float dyv[32];
@@ -416,7 +424,7 @@ template <bool F8, bool PAIR, int STAGES, int STAGE_BYTES>
 __device__ __forceinline__ void mma_issue_loop(uint32_t stage0_addr, uint64_t* full, uint64_t* empty,
                                                uint64_t* tmem_full, uint64_t* tmem_empty, uint32_t tmem_base,
                                                uint32_t idesc, int my_tiles, int k_blocks, volatile int* abort_flag,
-                                               int* status, int code_tmem, int code_full) {
+                                               Fc1Sink sink, int code_tmem, int code_full) {
   const uint32_t a_lo0 = static_cast<uint32_t>(umma_desc(stage0_addr));
   const uint32_t b_lo0 = static_cast<uint32_t>(umma_desc(stage0_addr + kATileBytes));
   const uint32_t hi = static_cast<uint32_t>(umma_desc(stage0_addr) >> 32);
@@ -430,11 +438,11 @@ __device__ __forceinline__ void mma_issue_loop(uint32_t stage0_addr, uint64_t* f
     for (int st = 0; st < STAGES; ++st) {
       if (it0 + st >= total_it) break;
       if (kb == 0) {  // first stage of a tile: its accumulator must have been drained by the epilogue
-        ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, status, code_tmem);
+        ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, sink, code_tmem);
         if (!ok) break;
       }
       if (!ready) {
-        ok = mbar_wait(&full[st], phase, abort_flag, status, code_full);
+        ok = mbar_wait(&full[st], phase, abort_flag, sink, code_full);
         if (!ok) break;
       }
       tc_fence_after();
@@ -521,7 +529,7 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
         const int nb0 = GATED == 1 ? ni * 128 : ni * kBN;
         const int nb1 = GATED == 1 ? a.n_out + ni * 128 : ni * kBN + 128;
         for (int kb = 0; kb < a.k_blocks; ++kb) {
-          ok = mbar_wait_timed(&s.empty[stage], phase ^ 1u, abort_flag, a.status, 1, tr0);
+          ok = mbar_wait_timed(&s.empty[stage], phase ^ 1u, abort_flag, a.sink, 1, tr0);
           if (!ok) break;
           mbar_expect_tx(&s.full[stage], kStageBytes);
           uint8_t* base = s.stage[stage];
@@ -553,7 +561,7 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
           static_cast<int>(blockIdx.x) < total_tiles ? (total_tiles - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1 : 0;
       mma_issue_loop<F8, false, kS, kStageBytes>(smem_u32(s.stage[0]), s.full, s.empty, s.tmem_full, s.tmem_empty,
                                                        tmem_base, umma_idesc(ABF), my_tiles, a.k_blocks, abort_flag,
-                                                       a.status, 2, 3);
+                                                       a.sink, 2, 3);
     }
     __syncwarp();
   } else {
@@ -573,7 +581,7 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
       tile_coords(a, t, mi, ni);
       float* sb = s.bias[warp - 2];
       stage_bias<GATED, OUT>(a, sb, ni, lane);
-      ok = __all_sync(0xffffffffu, mbar_wait_timed(&s.tmem_full[acc], acc_phase, abort_flag, a.status, 4, tr3));
+      ok = __all_sync(0xffffffffu, mbar_wait_timed(&s.tmem_full[acc], acc_phase, abort_flag, a.sink, 4, tr3));
       const long long t_busy0 = tr3 != nullptr ? clock64() : 0;
       if (!ok) break;
       tc_fence_after();
@@ -739,7 +747,7 @@ fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         const int nb =
             GATED == 1 ? (rank == 0 ? ni * 128 : a.n_out + ni * 128) : ni * kBN + static_cast<int>(rank) * 128;
         for (int kb = 0; kb < a.k_blocks; ++kb) {
-          ok = mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag, a.status, 11);
+          ok = mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag, a.sink, 11);
           if (!ok) break;
           if (rank == 0) mbar_expect_tx(&s.full[stage], 2 * kPairStageBytes);  // both CTAs' bytes
           const uint32_t leader_full = mapa_u32(smem_u32(&s.full[stage]), 0);
@@ -768,7 +776,7 @@ fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       const int my_tiles = first_tile < total_tiles ? (total_tiles - 1 - first_tile) / tile_step + 1 : 0;
       mma_issue_loop<F8, true, kPairStages, kPairStageBytes>(smem_u32(s.stage[0]), s.full, s.empty, s.tmem_full,
                                                               s.tmem_empty, tmem_base, umma_idesc_pair(ABF), my_tiles,
-                                                              a.k_blocks, abort_flag, a.status, 12, 13);
+                                                              a.k_blocks, abort_flag, a.sink, 12, 13);
     }
     __syncwarp();
   } else if (warp >= 2) {
@@ -785,7 +793,7 @@ fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       pair_tile_coords(tiles_m2, a.tiles_n, t, mi, ni);
       float* sb = s.bias[warp - 2];
       stage_bias<GATED, OUT>(a, sb, ni, lane);
-      ok = __all_sync(0xffffffffu, mbar_wait(&s.tmem_full[acc], acc_phase, abort_flag, a.status, 14));
+      ok = __all_sync(0xffffffffu, mbar_wait(&s.tmem_full[acc], acc_phase, abort_flag, a.sink, 14));
       if (!ok) break;
       tc_fence_after();
       const int row0 = mi * 2 * kBM + static_cast<int>(rank) * kBM + q * 32;
@@ -905,7 +913,7 @@ extern "C" int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const
   if (m > INT32_MAX - kBM || n > INT32_MAX - kBN || k > INT32_MAX - 256) return ND_ERR_UNSUPPORTED;
 
   Fc1Args a{};
-  a.bias = bias; a.y = y; a.alpha_dev = alpha_dev; a.status = status; a.alpha_host = alpha_host;
+  a.bias = bias; a.y = y; a.alpha_dev = alpha_dev; a.sink = Fc1Sink{status, device_error_ptr()}; a.alpha_host = alpha_host;
   a.trace = g_fc1_trace.load(std::memory_order_relaxed);
   a.m = static_cast<int>(m); a.k = static_cast<int>(k); a.n = static_cast<int>(n);
   a.n_out = static_cast<int>(n_out);
@@ -1023,7 +1031,7 @@ extern "C" int nd_fc1_bwd_dz(int dtype, int act, const void* x, const void* w, c
   if (m > INT32_MAX - kBM || n > INT32_MAX - kBN || k > INT32_MAX - 256) return ND_ERR_UNSUPPORTED;
 
   Fc1Args a{};
-  a.bias = bias; a.y = dz; a.status = status; a.alpha_host = 1.f;
+  a.bias = bias; a.y = dz; a.sink = Fc1Sink{status, device_error_ptr()}; a.alpha_host = 1.f;
   a.m = static_cast<int>(m); a.k = static_cast<int>(k); a.n = static_cast<int>(n);
   a.n_out = static_cast<int>(n_out);
   a.tiles_m = static_cast<int>((m + kBM - 1) / kBM);

@@ -48,17 +48,22 @@ static size_t partial_slots(long long rows, long long row_start, long long seq_l
 static int check_shape(int64_t rows, int64_t row_start, int64_t seq_len, int64_t hidden) {
   if (rows < 0 || row_start < 0 || seq_len <= 0 || hidden <= 0) return ND_ERR_BAD_ARG;
   if (seq_len > INT32_MAX || hidden > INT32_MAX) return ND_ERR_UNSUPPORTED;
+  // every limit of the launches below is tested here, before the first kernel is enqueued: samples are a grid x
+  // extent (2^31 - 1), the column blocks of the second dparam stage a grid y extent (65535)
+  if (rows > 0 && (row_start + rows - 1) / seq_len - row_start / seq_len + 1 > INT32_MAX) return ND_ERR_UNSUPPORTED;
+  if ((2 * hidden + 127) / 128 > 65535) return ND_ERR_UNSUPPORTED;
   return ND_OK;
 }
 
-// Stage 2 of the dparam reduction (any element type: the partials are fp32). Sample `b_first + blockIdx.y`
-// owns the consecutive workspace slots [first, first + count); they are summed in index order.
+// Stage 2 of the dparam reduction (any element type: the partials are fp32). Sample `b_first + blockIdx.x`
+// (the grid's x extent has no practical limit: a 2-D input is one sample per row) owns the consecutive
+// workspace slots [first, first + count); they are summed in index order.
 //   chunk scheme (n_chunks > 0): slot = chunk + sample index, chunks = those that overlap the sample's rows;
 //   item scheme  (n_chunks == 0): slot = sample index * tiles_per_sample + tile.
 __global__ void __launch_bounds__(128) norm_dparam_stage2_kernel(const NormArgs a) {
   griddep_launch_dependents();
   griddep_wait();  // the partials come from the kernel launched just before
-  const long long bi = blockIdx.y;
+  const long long bi = blockIdx.x;
   const long long b = a.b_first + bi;
   const int H = a.hidden;
   long long first, count;
@@ -80,7 +85,7 @@ __global__ void __launch_bounds__(128) norm_dparam_stage2_kernel(const NormArgs 
     first = bi * a.tiles_per_sample;
     count = a.tiles_per_sample;
   }
-  const int colx = (blockIdx.x * blockDim.x + threadIdx.x);  // one column of [dscale | dshift] per thread
+  const int colx = (blockIdx.y * blockDim.x + threadIdx.x);  // one column of [dscale | dshift] per thread
   if (colx >= 2 * H) return;
   const float* src = a.ws_part + first * 2 * H + colx;
   const long long stride = 2LL * H;
@@ -107,8 +112,7 @@ __global__ void __launch_bounds__(128) norm_dparam_stage2_kernel(const NormArgs 
 
 int launch_dparam_stage2(const NormArgs& a, cudaStream_t st) {
   if (a.n_samples <= 0) return ND_OK;
-  if (a.n_samples > 65535) return ND_ERR_UNSUPPORTED;  // grid.y limit
-  const dim3 grid(static_cast<unsigned>((2 * a.hidden + 127) / 128), static_cast<unsigned>(a.n_samples));
+  const dim3 grid(static_cast<unsigned>(a.n_samples), static_cast<unsigned>((2 * a.hidden + 127) / 128));
   NormArgs copy = a;
   return launch_checked(reinterpret_cast<const void*>(norm_dparam_stage2_kernel), 0, 128, copy, 0, st, grid);
 }

@@ -221,3 +221,21 @@ def test_unsupported_shapes_are_rejected_not_mangled():
     # n_out = 4 is not a multiple of 8
     assert L.nd_fc1_fwd(capi.ND_BF16, capi.ND_BF16, 0, 1, x.data_ptr(), w.data_ptr(), None, 1.0, None,
                         y.data_ptr(), 8, 16, 8, None, st) == -2
+
+
+def test_fc1_launches_leave_the_device_error_word_clear():
+    """The FC1 kernels record an expired wait in the device error word (codes 101..) as well as in the caller's
+    status word, so that launches through the torch extension, which passes no status word, are covered by
+    nd_device_error() too. Nothing expires in a healthy run: after forward, FP8 forward and backward-dz launches
+    with NO status word the error word must still read zero."""
+    L = capi.lib()
+    assert L.nd_device_error(1) >= 0  # clear whatever an earlier test may have left
+    x, w, b = (t.to(DEV) for t in synth.fc1_inputs(512, 256, 512, torch.bfloat16, seed=4))
+    dy = torch.randn(512, 256, device=DEV).to(torch.bfloat16)
+    capi.fc1_fwd(x, w, b, "gelu", 1)            # status=None
+    capi.fc1_bwd_dz(x, w, b, dy, "gelu")        # status=None
+    qx, sx = capi.quantize_e4m3(x)
+    qw, sw = capi.quantize_e4m3(w)
+    capi.fc1_fwd(qx, qw, b, "silu", 0, alpha_dev=torch.cat([sx, sw]), out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    assert L.nd_device_error(0) == 0

@@ -53,6 +53,15 @@ def test_no_alloc_backward_refuses_what_does_not_fit():
     # hidden = 4096 needs (148 * 8 + B) slots of 32 KiB: far more than the built-in 16 MiB
     rows, s, h = 64, 8, 4096
     assert L.nd_norm_dparam_ws_bytes(rows, 0, s, h) > L.nd_noalloc_scratch_bytes()
-    rc = L.nd_adaln_bwd_noalloc(capi.ND_BF16, 1, 1, 1, 1, 1, 1, 1, 1, rows, 0, s, h, None)
+    # real tensors of the right sizes: if the size check ever regressed, the call would run on valid memory and
+    # show up as a wrong return code, not as a device fault
+    x, scale, dy, mean, invstd = _inputs(rows // s, s, h, 2)
+    dx = torch.empty_like(x)
+    dscale = torch.zeros(rows // s, h, dtype=torch.float32, device=DEV)
+    dshift = torch.zeros_like(dscale)
+    rc = L.nd_adaln_bwd_noalloc(capi.ND_BF16, dy.data_ptr(), x.data_ptr(), scale.data_ptr(), mean.data_ptr(),
+                                invstd.data_ptr(), dx.data_ptr(), dscale.data_ptr(), dshift.data_ptr(), rows, 0, s, h,
+                                torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
     assert rc == -6 and b"too large" in L.nd_status_string(rc)
     assert L.nd_adaln_bwd_noalloc(capi.ND_BF16, None, None, None, None, None, None, None, None, 0, 0, s, h, None) == 0
