@@ -575,7 +575,74 @@ def bench_sharded(dev, stream, rank: int, world: int, hbm_peak: float, tf_peak: 
                                          "frac_of_n_x_bf16_peak": total / ms / 1e9 / (world * tf_peak)}
         del g
     out["fc1_status_word"] = int(status.item())
+    del xc, wc, bc
+    out["dit_stack_config5"] = bench_dit_stack(dev, rank, world, max_over_ranks)
     return out if rank == 0 else None
+
+
+def bench_dit_stack(dev, rank: int, world: int, max_over_ranks) -> dict:
+    """Workload config 5: one training step (forward + backward with respect to x, c and every parameter) of the
+    DiT-XL/2 block stack - depth 28, hidden 1152, 16 heads, MLP ratio 4, adaLN-Zero modulation, x [32,256,1152] bf16
+    per GPU, random-init weights N(0, 0.02) - built from the REFERENCE's own NovaDiTBlock modules running on this
+    library's extension (novadit_b200/modules.py). The batch is sharded: every rank steps its own 32 samples, no
+    gradient all-reduce (that is ordinary data parallelism, outside the operator path). Rank 0 also steps the same
+    stack on the reference's PyTorch operator definitions for the parity figures and the speed-up."""
+    try:
+        from novadit_b200.modules import DiTStack, init_stack_, reference_modules
+
+        reference_modules()
+    except Exception as exc:
+        return {"unavailable": str(exc).splitlines()[0][:160]}
+    dt = torch.bfloat16
+    gen = torch.Generator().manual_seed(1000 + rank)
+    x = torch.randn(B, S, H, generator=gen).to(dev, dt).requires_grad_(True)
+    cond = torch.randn(B, H, generator=gen).to(dev, dt).requires_grad_(True)
+    dy = torch.randn(B, S, H, generator=gen).to(dev, dt)
+
+    def build(fused: bool):
+        stack = DiTStack(H, 16, 28, use_fused=fused, zero_init=False, device=dev, dtype=dt)
+        init_stack_(stack, seed=0, zero_init=False)
+        targets = (x, cond, *stack.parameters())
+
+        def step():
+            y = stack(x, cond)
+            return y, torch.autograd.grad(y, targets, dy)
+
+        return step
+
+    def median_ms(step, warm: int, iters: int) -> float:
+        for _ in range(warm):
+            step()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    fused_step = build(True)
+    ms = max_over_ranks(median_ms(fused_step, 2, 5))
+    res = {"ms_per_step": ms, "tokens_per_s_all_gpus": world * B * S / ms * 1e3, "tokens_per_gpu": B * S,
+           "blocks": "reference novadit.modules.NovaDiTBlock x 28 on novadit_cuda of this library"}
+    if rank == 0:
+        yf, gf = fused_step()
+        ref_step = build(False)
+        ref_ms = median_ms(ref_step, 1, 3)
+        yr, gr = ref_step()
+
+        def rel(a, b):
+            a, b = a.detach().float(), b.detach().float()
+            return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+        res.update({"pytorch_operators_ms_per_step_rank0": ref_ms, "speedup_vs_pytorch_operators": ref_ms / ms,
+                    "parity_rel_l2": {"y": rel(yf, yr), "dx": rel(gf[0], gr[0]), "dcond": rel(gf[1], gr[1]),
+                                      "param_grads": rel(torch.cat([g.flatten() for g in gf[2:]]),
+                                                         torch.cat([g.flatten() for g in gr[2:]]))}})
+    return res
 
 
 def bench_e2e(dev, k: int) -> dict:

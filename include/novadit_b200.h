@@ -81,6 +81,22 @@ int nd_adarms_fwd_e4m3(int dtype, const void* x, const void* scale, const void* 
                        float* inv_rms, const float* q_scale, float* amax, int64_t rows, int64_t row_start,
                        int64_t seq_len, int64_t hidden, float eps, void* stream);
 
+/* AdaLN / AdaRMSNorm forward with the gated residual of the block in front, in ONE pass:
+ *   x_new = x + gate[b] * branch   (gate NULL: x + branch), rounded once to the element type and written out,
+ *   y     = norm(x_new) * (1 + scale[b]) + shift[b], statistics of x_new as in nd_adaln_fwd.
+ * Bytes moved: 4 tensors of [rows, hidden] (x, branch in; x_new, y out) instead of the 5 of a residual kernel
+ * followed by a norm kernel; results are bit-identical to that composition (nd_gated_residual_fwd or
+ * nd_out_residual_fwd, then nd_adaln_fwd), which is also what runs for rows the one-pass kernel does not take
+ * (not 16-byte vectorisable, or wider than 512 vectors). The operators are specified in the reference
+ * (SPEC.md:293-376, novadit/ops/residual.py:8-25) but it has no fused kernel: no counterpart there. Backward:
+ * nd_adaln_bwd on x_new, then nd_gated_residual_bwd_add, which adds the residual stream's own gradient. */
+int nd_adaln_fwd_residual(int dtype, const void* x, const void* branch, const void* gate, const void* scale,
+                          const void* shift, void* x_new, void* y, float* mean, float* invstd, int64_t rows,
+                          int64_t row_start, int64_t seq_len, int64_t hidden, float eps, void* stream);
+int nd_adarms_fwd_residual(int dtype, const void* x, const void* branch, const void* gate, const void* scale,
+                           const void* shift, void* x_new, void* y, float* inv_rms, int64_t rows, int64_t row_start,
+                           int64_t seq_len, int64_t hidden, float eps, void* stream);
+
 /* dx = invstd * (dxhat - mean_h(dxhat) - xhat * mean_h(dxhat * xhat)), dxhat = dy * (1 + scale[b]).
  * Replaces the launcher behind fused_adaln_backward_dx, csrc/ops/adaln_kernel.cu:1147-1193
  * (kernel :473-582). */
@@ -211,6 +227,13 @@ size_t nd_gated_residual_ws_bytes(int64_t rows, int64_t row_start, int64_t seq_l
 int nd_gated_residual_bwd(int dtype, const void* dy, const void* branch, const void* gate, void* dbranch,
                           float* dgate_partials, int64_t rows, int64_t row_start, int64_t seq_len,
                           int64_t hidden, int64_t tile_rows, void* stream);
+/* The same with a second gradient of the residual sum added first: dsum = dy + dres (rounded once, written out:
+ * the gradient that flows on along the residual stream), dbranch = gate * dsum, partials of dsum * branch. It
+ * replaces the separate addition of the two gradients that reach x_new of nd_adaln_fwd_residual (from the norm
+ * and from the stream). No counterpart in the reference. */
+int nd_gated_residual_bwd_add(int dtype, const void* dy, const void* dres, const void* branch, const void* gate,
+                              void* dsum, void* dbranch, float* dgate_partials, int64_t rows, int64_t row_start,
+                              int64_t seq_len, int64_t hidden, int64_t tile_rows, void* stream);
 
 /* -------------------------------------------------------------------- FC1 */
 

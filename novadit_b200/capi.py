@@ -68,6 +68,12 @@ SIGNATURES = {
     "nd_qkv_pack_bwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "nd_gated_residual_fwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, *_SHAPE4, c_void_p]),
     "nd_gated_residual_ws_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int64]),
+    "nd_adaln_fwd_residual": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, *_SHAPE4, c_float, c_void_p]),
+    "nd_adarms_fwd_residual": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, *_SHAPE4, c_float, c_void_p]),
+    "nd_gated_residual_bwd_add": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          *_SHAPE4, c_int64, c_void_p]),
     "nd_gated_residual_bwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, *_SHAPE4, c_int64,
                                       c_void_p]),
     "nd_fc1_fwd": (c_int, [c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float,
@@ -324,6 +330,48 @@ def gated_residual_bwd(dy, branch, gate, *, row_start=0, seq_len=None):
     check(L.nd_gated_residual_bwd(DTYPE_IDS[dy.dtype], _ptr(dy), _ptr(branch), _ptr(gate), _ptr(dbranch), _ptr(part),
                                   rows, row_start, seq_len, hidden, GATED_TILE_ROWS, _stream()), "nd_gated_residual_bwd")
     return dbranch, part
+
+
+def gated_residual_bwd_add(dy, dres, branch, gate, *, row_start=0, seq_len=None):
+    """(dsum = dy + dres, dbranch = gate * dsum, dgate_partials of dsum * branch)."""
+    _need_cuda(dy, dres, branch, gate)
+    hidden = dy.shape[-1]
+    if seq_len is None:
+        seq_len = dy.shape[1] if dy.dim() == 3 else 1
+    rows = dy.numel() // hidden
+    L = lib()
+    nbytes = L.nd_gated_residual_ws_bytes(rows, row_start, seq_len, hidden, GATED_TILE_ROWS)
+    tiles = (seq_len + GATED_TILE_ROWS - 1) // GATED_TILE_ROWS
+    part = torch.empty(nbytes // (4 * hidden * tiles), tiles, hidden, dtype=torch.float32, device=dy.device)
+    dsum, dbranch = torch.empty_like(dy), torch.empty_like(dy)
+    check(L.nd_gated_residual_bwd_add(DTYPE_IDS[dy.dtype], _ptr(dy), _ptr(dres), _ptr(branch), _ptr(gate), _ptr(dsum),
+                                      _ptr(dbranch), _ptr(part), rows, row_start, seq_len, hidden, GATED_TILE_ROWS,
+                                      _stream()), "nd_gated_residual_bwd_add")
+    return dsum, dbranch, part
+
+
+def norm_fwd_residual(kind, x, branch, gate, scale, shift, eps, *, stats=True, row_start=0, seq_len=None):
+    """x_new = x + gate[b] * branch (gate None: x + branch) and its AdaLN ("layer") / AdaRMSNorm ("rms") in one
+    pass. Returns (x_new, y, mean, invstd) / (x_new, y, inv_rms)."""
+    _need_cuda(x, branch, gate, scale, shift)
+    hidden = x.shape[-1]
+    if seq_len is None:
+        seq_len = x.shape[1] if x.dim() == 3 else 1
+    rows = x.numel() // hidden
+    x_new, y = torch.empty_like(x), torch.empty_like(x)
+    lead = x.shape[:-1]
+    dt = DTYPE_IDS[x.dtype]
+    invstd = torch.empty(lead, dtype=torch.float32, device=x.device) if stats else None
+    if kind == "layer":
+        mean = torch.empty(lead, dtype=torch.float32, device=x.device) if stats else None
+        check(lib().nd_adaln_fwd_residual(dt, _ptr(x), _ptr(branch), _ptr(gate), _ptr(scale), _ptr(shift), _ptr(x_new),
+                                          _ptr(y), _ptr(mean), _ptr(invstd), rows, row_start, seq_len, hidden, eps,
+                                          _stream()), "nd_adaln_fwd_residual")
+        return x_new, y, mean, invstd
+    check(lib().nd_adarms_fwd_residual(dt, _ptr(x), _ptr(branch), _ptr(gate), _ptr(scale), _ptr(shift), _ptr(x_new),
+                                       _ptr(y), _ptr(invstd), rows, row_start, seq_len, hidden, eps, _stream()),
+          "nd_adarms_fwd_residual")
+    return x_new, y, invstd
 
 
 # ---------------------------------------------------------------- FC1

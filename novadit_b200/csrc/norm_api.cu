@@ -146,6 +146,33 @@ static int norm_fwd(bool rms, int dtype, const void* x, const void* scale, const
   return dispatch(dtype, a, stream);
 }
 
+int gated_residual_fwd_any(int dtype, const void* x, const void* branch, const void* gate, void* y, int64_t rows,
+                           int64_t row_start, int64_t seq_len, int64_t hidden, void* stream);  // rowops.cu
+
+// Forward with the gated residual in front: x_new = x + gate[b] * branch (gate null: x + branch), then the norm of
+// x_new. One kernel where the bulk-copy kernels apply, else the residual kernel followed by the norm kernel
+// (identical results: both round x_new once and normalise the rounded values).
+static int norm_fwd_residual(bool rms, int dtype, const void* x, const void* branch, const void* gate, const void* scale,
+                             const void* shift, void* x_new, void* y, float* mean, float* invstd, int64_t rows,
+                             int64_t row_start, int64_t seq_len, int64_t hidden, float eps, void* stream) {
+  if (int s = check_shape(rows, row_start, seq_len, hidden)) return s;
+  if (rows == 0) return ND_OK;
+  if (!x || !branch || !scale || !shift || !x_new || !y) return ND_ERR_BAD_ARG;
+  if (!rms && ((mean == nullptr) != (invstd == nullptr))) return ND_ERR_BAD_ARG;
+  NormArgs a{};
+  a.x = x; a.dy = branch; a.gate = gate; a.dx = x_new; a.res = true;
+  a.scale = scale; a.shift = shift; a.y = y;
+  a.mean = rms ? nullptr : mean;
+  a.invstd = invstd;
+  a.rows = rows; a.row_start = row_start;
+  a.seq_len = static_cast<int>(seq_len); a.hidden = static_cast<int>(hidden);
+  a.eps = eps; a.mode = kFwd; a.rms = rms;
+  const int s = dispatch(dtype, a, stream);
+  if (s != ND_ERR_UNSUPPORTED) return s;
+  if (int r = gated_residual_fwd_any(dtype, x, branch, gate, x_new, rows, row_start, seq_len, hidden, stream)) return r;
+  return norm_fwd(rms, dtype, x_new, scale, shift, y, mean, invstd, rows, row_start, seq_len, hidden, eps, stream);
+}
+
 static int norm_bwd(bool rms, int mode, int dtype, const void* dy, const void* x,
                     const void* scale, const float* mean, const float* invstd, void* dx,
                     float* dscale, float* dshift, int64_t rows, int64_t row_start,
@@ -222,6 +249,20 @@ int nd_adarms_fwd_e4m3(int dtype, const void* x, const void* scale, const void* 
   if (!q_scale) return ND_ERR_BAD_ARG;
   return norm_fwd(true, dtype, x, scale, shift, q, nullptr, inv_rms, rows, row_start, seq_len, hidden, eps, stream,
                   q_scale, amax);
+}
+
+int nd_adaln_fwd_residual(int dtype, const void* x, const void* branch, const void* gate, const void* scale,
+                          const void* shift, void* x_new, void* y, float* mean, float* invstd, int64_t rows,
+                          int64_t row_start, int64_t seq_len, int64_t hidden, float eps, void* stream) {
+  return norm_fwd_residual(false, dtype, x, branch, gate, scale, shift, x_new, y, mean, invstd, rows, row_start,
+                           seq_len, hidden, eps, stream);
+}
+
+int nd_adarms_fwd_residual(int dtype, const void* x, const void* branch, const void* gate, const void* scale,
+                           const void* shift, void* x_new, void* y, float* inv_rms, int64_t rows, int64_t row_start,
+                           int64_t seq_len, int64_t hidden, float eps, void* stream) {
+  return norm_fwd_residual(true, dtype, x, branch, gate, scale, shift, x_new, y, nullptr, inv_rms, rows, row_start,
+                           seq_len, hidden, eps, stream);
 }
 
 int nd_adaln_bwd_dx(int dtype, const void* dy, const void* x, const void* scale,

@@ -55,6 +55,10 @@ struct NormArgs {
   // *q_amax = max(*q_amax, max |value|) (nullable)
   const float* q_scale;
   float* q_amax;
+  // forward with the gated residual in front (bulk-copy kernels only): x_new = x + gate[b] * branch is written to dx
+  // and normalised; `dy` holds branch, `gate` the [B, H] gate (null: plain x + branch), `res` switches it on
+  const void* gate;
+  bool res;
 };
 
 // first row (local to the shard) of chunk c

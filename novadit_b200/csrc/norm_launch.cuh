@@ -125,20 +125,22 @@ int launch_norm_tma(NormArgs a, cudaStream_t st) {
   }
   // forward of a large tensor (128 MB and up): one warp per row; measured faster there and slower below
   const bool large = static_cast<double>(a.rows) * a.hidden * sizeof(T) >= 128.0 * 1024 * 1024;
-  if (a.mode == kFwd && (norm_variant() == 4 || (large && norm_variant() != 3))) {
+  if (a.mode == kFwd && !a.res && (norm_variant() == 4 || (large && norm_variant() != 3))) {
     if (const void* fw = pick_fwd_warp<T, VEC>(a.hidden / VEC, a.rms)) return launch_norm_fwd_warp<T, VEC>(a, fw, st);
   }
   constexpr int RPI = 4;
   const int nvec = a.hidden / VEC;
   const int nt = (nvec + 31) / 32 * 32;
   // 128 registers per backward thread: three 160-thread CTAs per SM, and 512-thread CTAs still launch
-  const void* fn = pick_tma<T, VEC, RPI, 96, 128>(a.mode, a.rms);
-  // as many pipeline stages as fit the per-CTA shared-memory budget (4 forward / 3 backward CTAs per SM)
-  const int tensors = a.mode == kFwd ? 1 : 2;
+  const void* fn = pick_tma<T, VEC, RPI, 96, 128>(a.mode, a.rms, a.res);
+  // as many pipeline stages as fit the per-CTA shared-memory budget (4 forward / 3 backward CTAs per SM; the
+  // forward with the residual in front stages two tensors and has the backward's footprint)
+  const bool light = a.mode == kFwd && !a.res;
+  const int tensors = light ? 1 : 2;
   const int stage_bytes = tensors * RPI * a.hidden * static_cast<int>(sizeof(T));
   // Two stages measured best at the DiT-XL/2 shape: deeper pipelines hold shared memory that the
   // next kernel's CTAs (programmatic dependent launch) could otherwise start in. Never more than fits.
-  const int budget = a.mode == kFwd ? 54 * 1024 : 72 * 1024;
+  const int budget = light ? 54 * 1024 : 72 * 1024;
   int stages = norm_stages_override() > 0 ? norm_stages_override() : 2;
   if (stages > budget / stage_bytes) stages = budget / stage_bytes;
   if (stages < 2) stages = 2;
@@ -151,7 +153,7 @@ int launch_norm_tma(NormArgs a, cudaStream_t st) {
     (void)cudaGetLastError();
     return ND_ERR_LAUNCH;
   }
-  long long chunks = resident_slots(fn, nt, smem, a.mode == kFwd);
+  long long chunks = resident_slots(fn, nt, smem, light);
   const long long most = a.rows / RPI > 1 ? a.rows / RPI : 1;  // every chunk holds at least one full group
   if (chunks > most) chunks = most;
   plan_chunks(a, chunks, RPI);
@@ -204,9 +206,11 @@ template <typename T>
 int launch_norm(NormArgs a, cudaStream_t st) {
   constexpr int VMAX = 16 / sizeof(T);
   bool vec_ok = (a.hidden % VMAX) == 0;
-  const void* ptrs[] = {a.x, a.scale, a.shift, a.y, a.dy, a.dx, a.dscale, a.dshift, a.ws_part};
+  const void* ptrs[] = {a.x, a.scale, a.shift, a.y, a.dy, a.dx, a.dscale, a.dshift, a.ws_part, a.gate};
   for (const void* p : ptrs) vec_ok = vec_ok && aligned16(p);
   a.err = device_error_ptr();
+  // the residual in front of the norm exists in the bulk-copy kernels only: the caller composes the two operators
+  if (a.res && (!vec_ok || a.hidden / VMAX > 512 || norm_variant() == 1)) return ND_ERR_UNSUPPORTED;
   if (!vec_ok) return a.q_scale != nullptr ? ND_ERR_UNSUPPORTED : launch_norm_generic<T, 1>(a, st);
   if (a.q_scale != nullptr && a.hidden / VMAX > 192) return ND_ERR_UNSUPPORTED;
   if (a.q_scale != nullptr || (a.hidden / VMAX <= 512 && norm_variant() != 1)) return launch_norm_tma<T, VMAX>(a, st);

@@ -114,7 +114,11 @@ __device__ __forceinline__ void drain_after_abort() {
   while (global_ns() - t0 < 200000ull) __nanosleep(1000);
 }
 
-template <typename T, int VEC, int RPI, int MAXR, bool RMS>
+// RES: the input of the normalisation is the gated residual x + gate[b] * branch (gate null: x + branch), which is
+// written out as well (a.dx = x_new; a.dy = branch): one pass instead of a residual kernel followed by a norm
+// kernel. The sum is rounded to T first and the statistics are taken of the ROUNDED values, so that y, mean and
+// 1/std are exactly what the norm of the stored x_new gives.
+template <typename T, int VEC, int RPI, int MAXR, bool RMS, bool RES = false>
 __global__ void __maxnreg__(MAXR) norm_fwd_tma(const NormArgs a) {
   constexpr int NP = VEC / 2;
   extern __shared__ __align__(128) unsigned char dsm[];
@@ -129,10 +133,11 @@ __global__ void __maxnreg__(MAXR) norm_fwd_tma(const NormArgs a) {
 
   const int H = a.hidden;
   const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
-  const uint32_t stage_total = RPI * row_bytes;
+  const uint32_t stage_total = (RES ? 2 : 1) * RPI * row_bytes;  // x rows [then branch rows]
   const bool active = tid < H / VEC;
   const int col = active ? tid * VEC : 0;
   const uint32_t src_stride = active ? row_bytes : 0u;
+  const uint32_t br_off = active ? RPI * row_bytes : 0u;
   const float inv_h = 1.f / static_cast<float>(H);
   const float eps = a.eps;
   const long long row_elems = H;
@@ -140,7 +145,7 @@ __global__ void __maxnreg__(MAXR) norm_fwd_tma(const NormArgs a) {
 
   GroupCursor pc;
   bool pc_valid;
-  pipeline_start<T, RPI, false>(a, full, buf, row_bytes, pc, pc_valid);
+  pipeline_start<T, RPI, RES>(a, full, buf, row_bytes, pc, pc_valid);
 
   int stage = 0;
   uint32_t parity = 0;
@@ -159,6 +164,16 @@ __global__ void __maxnreg__(MAXR) norm_fwd_tma(const NormArgs a) {
 #pragma unroll
       for (int i = 0; i < NP; ++i) sc[i] = __fadd2_rn(sc[i], make_float2(1.f, 1.f));
     }
+    [[maybe_unused]] float2 gt[NP];
+    if constexpr (RES) {
+#pragma unroll
+      for (int i = 0; i < NP; ++i) gt[i] = make_float2(1.f, 1.f);
+      if (a.gate != nullptr) {
+        Vec<T, VEC> vg;
+        vg.load(static_cast<const T*>(a.gate) + b * H + col);
+        unpack2<T, VEC>(vg, gt);
+      }
+    }
     do {
       const long long r = cc.r;
       const int nrows = cc.group_rows(RPI);
@@ -175,6 +190,17 @@ __global__ void __maxnreg__(MAXR) norm_fwd_tma(const NormArgs a) {
         Vec<T, VEC> pk;
         *reinterpret_cast<uint4*>(pk.v) = *reinterpret_cast<const uint4*>(src + j * src_stride);
         unpack2<T, VEC>(pk, X[j]);
+        if constexpr (RES) {
+          Vec<T, VEC> pb;
+          *reinterpret_cast<uint4*>(pb.v) = *reinterpret_cast<const uint4*>(src + br_off + j * src_stride);
+          float2 Bv[NP];
+          unpack2<T, VEC>(pb, Bv);
+#pragma unroll
+          for (int i = 0; i < NP; ++i) X[j][i] = __ffma2_rn(gt[i], Bv[i], X[j][i]);
+          pack2<T, VEC>(X[j], pk);  // the one rounding of the residual stream
+          if (active && j < nrows) pk.store(static_cast<T*>(a.dx) + (r + j) * row_elems + col);
+          unpack2<T, VEC>(pk, X[j]);  // the norm sees what was stored
+        }
       }
 
       float mean_mine[1] = {0.f};
@@ -197,7 +223,7 @@ __global__ void __maxnreg__(MAXR) norm_fwd_tma(const NormArgs a) {
         }
         if (tid == 0 && pc_valid) {  // every thread has read the stage: refill it
           fence_proxy_async_smem();
-          issue_group<T, RPI, false>(a, pc, stage, full, buf, row_bytes);
+          issue_group<T, RPI, RES>(a, pc, stage, full, buf, row_bytes);
           pc_valid = pc.next(a, RPI);
         }
         refilled = true;
@@ -226,7 +252,7 @@ __global__ void __maxnreg__(MAXR) norm_fwd_tma(const NormArgs a) {
       }
       if (!refilled && tid == 0 && pc_valid) {
         fence_proxy_async_smem();
-        issue_group<T, RPI, false>(a, pc, stage, full, buf, row_bytes);
+        issue_group<T, RPI, RES>(a, pc, stage, full, buf, row_bytes);
         pc_valid = pc.next(a, RPI);
       }
 
@@ -432,7 +458,9 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma(const NormArgs a) {
 }
 
 template <typename T, int VEC, int RPI, int MAXRF, int MAXRB>
-static const void* pick_tma(int mode, bool rms) {
+static const void* pick_tma(int mode, bool rms, bool res = false) {
+  if (mode == kFwd && res)
+    return rms ? (const void*)norm_fwd_tma<T, VEC, RPI, MAXRB, true, true> : (const void*)norm_fwd_tma<T, VEC, RPI, MAXRB, false, true>;
   switch (mode) {
     case kFwd:
       return rms ? (const void*)norm_fwd_tma<T, VEC, RPI, MAXRF, true> : (const void*)norm_fwd_tma<T, VEC, RPI, MAXRF, false>;

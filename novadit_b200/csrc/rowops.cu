@@ -90,6 +90,8 @@ struct GatedArgs {
   const void* gate;  // [batch, hidden]
   void* out;         // forward: y; backward: dbranch
   float* part;       // backward: [batch_in_shard * tiles_per_sample, hidden] fp32
+  const void* add;   // backward, nullable: a second gradient of the same tensor, added to dy first
+  void* sum_out;     // backward with `add`: dy + add, rounded once (what flows on along the residual stream)
   long long rows, row_start;
   int seq_len, hidden, tile_rows, tiles_per_sample;
   long long b_first;
@@ -112,6 +114,8 @@ __global__ void __launch_bounds__(256) gated_residual_kernel(const GatedArgs g) 
   const T* __restrict__ pa = static_cast<const T*>(g.a);
   const T* __restrict__ pb = static_cast<const T*>(g.b);
   T* __restrict__ po = static_cast<T*>(g.out);
+  [[maybe_unused]] const T* __restrict__ padd = static_cast<const T*>(g.add);
+  [[maybe_unused]] T* __restrict__ psum = static_cast<T*>(g.sum_out);
   for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
     Vec<T, VEC> vg;
     vg.load(static_cast<const T*>(g.gate) + b * g.hidden + v * VEC);
@@ -136,6 +140,19 @@ __global__ void __launch_bounds__(256) gated_residual_kernel(const GatedArgs g) 
           float fa[VEC], fb[VEC], fo[VEC];
           va[j].unpack(fa);
           vb[j].unpack(fb);
+          if constexpr (BWD) {
+            if (padd != nullptr) {  // dy + add, rounded to T as the separate addition would: the rest uses that value
+              Vec<T, VEC> vd;
+              vd.load_stream(padd + (r + j) * g.hidden + v * VEC);
+              float fd[VEC];
+              vd.unpack(fd);
+#pragma unroll
+              for (int k = 0; k < VEC; ++k) fa[k] += fd[k];
+              vd.pack(fa);
+              vd.store(psum + (r + j) * g.hidden + v * VEC);
+              vd.unpack(fa);
+            }
+          }
 #pragma unroll
           for (int k = 0; k < VEC; ++k) {
             if constexpr (BWD) {
@@ -216,12 +233,13 @@ static int qkv_entry(int dtype, bool pack, void* qkv, void* q, void* k, void* v,
 
 static int gated_entry(int dtype, bool bwd, const void* a, const void* b, const void* gate, void* out, float* part,
                        int64_t rows, int64_t row_start, int64_t seq_len, int64_t hidden, int64_t tile_rows,
-                       void* stream) {
+                       void* stream, const void* add = nullptr, void* sum_out = nullptr) {
   if (rows < 0 || row_start < 0 || seq_len <= 0 || hidden <= 0 || tile_rows <= 0) return ND_ERR_BAD_ARG;
   if (hidden > INT32_MAX || seq_len > INT32_MAX || tile_rows > INT32_MAX) return ND_ERR_UNSUPPORTED;
   if (rows == 0) return ND_OK;
-  if (!a || !b || !gate || !out || (bwd && !part)) return ND_ERR_BAD_ARG;
+  if (!a || !b || !gate || !out || (bwd && !part) || ((add != nullptr) != (sum_out != nullptr))) return ND_ERR_BAD_ARG;
   GatedArgs g{};
+  g.add = add; g.sum_out = sum_out;
   g.a = a; g.b = b; g.gate = gate; g.out = out; g.part = part;
   g.rows = rows; g.row_start = row_start;
   g.seq_len = static_cast<int>(seq_len); g.hidden = static_cast<int>(hidden);
@@ -236,7 +254,7 @@ static int gated_entry(int dtype, bool bwd, const void* a, const void* b, const 
     using T = decltype(tag);
     constexpr int VMAX = 16 / sizeof(T);
     const bool vec_ok = g.hidden % VMAX == 0 && aligned16(a) && aligned16(b) && aligned16(gate) && aligned16(out) &&
-                        (!bwd || aligned16(part));
+                        (!bwd || aligned16(part)) && aligned16(add) && aligned16(sum_out);
     const void* fn;
     if (vec_ok) fn = bwd ? (const void*)gated_residual_kernel<T, VMAX, true> : (const void*)gated_residual_kernel<T, VMAX, false>;
     else fn = bwd ? (const void*)gated_residual_kernel<T, 1, true> : (const void*)gated_residual_kernel<T, 1, false>;
@@ -282,6 +300,14 @@ int nd_gated_residual_bwd(int dtype, const void* dy, const void* branch, const v
 }
 
 
+int nd_gated_residual_bwd_add(int dtype, const void* dy, const void* dres, const void* branch, const void* gate,
+                              void* dsum, void* dbranch, float* dgate_partials, int64_t rows, int64_t row_start,
+                              int64_t seq_len, int64_t hidden, int64_t tile_rows, void* stream) {
+  if (!dres || !dsum) return ND_ERR_BAD_ARG;
+  return nd::gated_entry(dtype, true, dy, branch, gate, dbranch, dgate_partials, rows, row_start, seq_len, hidden,
+                         tile_rows, stream, dres, dsum);
+}
+
 int nd_out_residual_fwd(int dtype, const void* x, const void* residual, const void* bias, void* y, int64_t rows,
                         int64_t hidden, void* stream) {
   using namespace nd;
@@ -311,3 +337,15 @@ int nd_qkv_pack_bwd(int dtype, const void* dq, const void* dk, const void* dv, v
 }
 
 }  // extern "C"
+
+namespace nd {
+
+// x + gate[b] * branch, or x + branch when there is no gate: the composed path of the norm forward with the
+// residual in front, for rows the one-kernel version does not take
+int gated_residual_fwd_any(int dtype, const void* x, const void* branch, const void* gate, void* y, int64_t rows,
+                           int64_t row_start, int64_t seq_len, int64_t hidden, void* stream) {
+  if (gate == nullptr) return nd_out_residual_fwd(dtype, x, branch, nullptr, y, rows, hidden, stream);
+  return nd_gated_residual_fwd(dtype, x, branch, gate, y, rows, row_start, seq_len, hidden, stream);
+}
+
+}  // namespace nd

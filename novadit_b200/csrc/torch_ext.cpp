@@ -447,9 +447,212 @@ at::Tensor fused_out_residual_forward(const at::Tensor& x, const at::Tensor& res
   return y;
 }
 
+// ------------------------------------------------------------------ added operators (no counterpart in the reference)
+// Every function below validates and allocates like the ones above; they exist so that the Python operators of
+// novadit_b200.ops reach the C ABI through this module (checks, device guard, torch's stream) and never around it.
+
+void check_gate(const at::Tensor& gate, const at::Tensor& x) {
+  ND_CHECK_INPUT(gate);
+  TORCH_CHECK(gate.dim() == 2 && gate.size(0) == x.size(0) && gate.size(1) == x.size(2), "gate must have shape [B, H]");
+  TORCH_CHECK(gate.scalar_type() == x.scalar_type(), "gate and x must have the same dtype");
+  TORCH_CHECK(gate.device() == x.device(), "gate must be on x's device");
+}
+
+void check_same(const at::Tensor& t, const at::Tensor& x, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous(), name, " must be a contiguous CUDA tensor");
+  TORCH_CHECK(t.sizes() == x.sizes() && t.scalar_type() == x.scalar_type() && t.device() == x.device(), name,
+              " must have x's shape, dtype and device");
+}
+
+// x_new = x + gate * branch (gate optional) and its norm in one pass -> [x_new, y, scale[B,H], mean, invstd] (AdaLN)
+// or [x_new, y, scale[B,H], inv_rms] (AdaRMSNorm)
+std::vector<at::Tensor> residual_norm_forward(bool rms, const at::Tensor& x, const at::Tensor& branch,
+                                              c10::optional<at::Tensor> gate, const at::Tensor& scale,
+                                              const at::Tensor& shift, double eps) {
+  check_norm_inputs(x, scale, shift);
+  check_same(branch, x, "branch");
+  const void* gate_p = nullptr;
+  if (gate.has_value() && gate->defined()) {
+    check_gate(*gate, x);
+    gate_p = gate->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t B = x.size(0), S = x.size(1), H = x.size(2);
+  at::Tensor scale_c = scale.reshape({B, H}).contiguous(), shift_c = shift.reshape({B, H}).contiguous();
+  at::Tensor x_new = at::empty_like(x), y = at::empty_like(x);
+  auto stat_opts = x.options().dtype(at::kFloat).requires_grad(false);
+  at::Tensor invstd = at::empty({B, S}, stat_opts), mean;
+  int st;
+  if (rms) {
+    st = nd_adarms_fwd_residual(dtype_id(x), x.data_ptr(), branch.data_ptr(), gate_p, scale_c.data_ptr(), shift_c.data_ptr(),
+                                x_new.data_ptr(), y.data_ptr(), invstd.data_ptr<float>(), B * S, 0, S, H,
+                                static_cast<float>(eps), current_stream(x));
+  } else {
+    mean = at::empty({B, S}, stat_opts);
+    st = nd_adaln_fwd_residual(dtype_id(x), x.data_ptr(), branch.data_ptr(), gate_p, scale_c.data_ptr(), shift_c.data_ptr(),
+                               x_new.data_ptr(), y.data_ptr(), mean.data_ptr<float>(), invstd.data_ptr<float>(), B * S, 0,
+                               S, H, static_cast<float>(eps), current_stream(x));
+  }
+  check_status(st, rms ? "fused_residual_adarmsnorm_forward" : "fused_residual_adaln_forward");
+  if (rms) return {x_new, y, scale_c, invstd};
+  return {x_new, y, scale_c, mean, invstd};
+}
+std::vector<at::Tensor> fused_residual_adaln_forward(const at::Tensor& x, const at::Tensor& branch,
+                                                     c10::optional<at::Tensor> gate, const at::Tensor& scale,
+                                                     const at::Tensor& shift, double eps) {
+  return residual_norm_forward(false, x, branch, gate, scale, shift, eps);
+}
+std::vector<at::Tensor> fused_residual_adarmsnorm_forward(const at::Tensor& x, const at::Tensor& branch,
+                                                          c10::optional<at::Tensor> gate, const at::Tensor& scale,
+                                                          const at::Tensor& shift, double eps) {
+  return residual_norm_forward(true, x, branch, gate, scale, shift, eps);
+}
+
+constexpr int64_t kGatedTileRows = 8;
+
+at::Tensor fused_gated_residual_forward(const at::Tensor& x, const at::Tensor& branch, const at::Tensor& gate) {
+  ND_CHECK_INPUT(x);
+  TORCH_CHECK(x.dim() == 3 && dtype_id(x) >= 0, "x must be a [B, S, H] fp32/fp16/bf16 tensor");
+  check_same(branch, x, "branch");
+  check_gate(gate, x);
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor y = at::empty_like(x);
+  check_status(nd_gated_residual_fwd(dtype_id(x), x.data_ptr(), branch.data_ptr(), gate.data_ptr(), y.data_ptr(),
+                                     x.size(0) * x.size(1), 0, x.size(1), x.size(2), current_stream(x)),
+               "fused_gated_residual_forward");
+  return y;
+}
+
+// backward of y = x + gate * branch for the incoming gradient dy, optionally with a second gradient `dres` of y added
+// first: -> [dsum (= dy when there is no dres), dbranch, dgate [B, H] fp32]
+std::vector<at::Tensor> fused_gated_residual_backward(const at::Tensor& dy, c10::optional<at::Tensor> dres,
+                                                      const at::Tensor& branch, const at::Tensor& gate) {
+  ND_CHECK_INPUT(dy);
+  TORCH_CHECK(dy.dim() == 3 && dtype_id(dy) >= 0, "dy must be a [B, S, H] fp32/fp16/bf16 tensor");
+  check_same(branch, dy, "branch");
+  check_gate(gate, dy);
+  const bool add = dres.has_value() && dres->defined();
+  if (add) check_same(*dres, dy, "dres");
+  c10::cuda::CUDAGuard guard(dy.device());
+  const int64_t B = dy.size(0), S = dy.size(1), H = dy.size(2);
+  const int64_t tiles = (S + kGatedTileRows - 1) / kGatedTileRows;
+  at::Tensor part = at::empty({B, tiles, H}, dy.options().dtype(at::kFloat));
+  at::Tensor dbranch = at::empty_like(dy), dsum = add ? at::empty_like(dy) : dy;
+  int st;
+  if (add) {
+    st = nd_gated_residual_bwd_add(dtype_id(dy), dy.data_ptr(), dres->data_ptr(), branch.data_ptr(), gate.data_ptr(),
+                                   dsum.data_ptr(), dbranch.data_ptr(), part.data_ptr<float>(), B * S, 0, S, H,
+                                   kGatedTileRows, current_stream(dy));
+  } else {
+    st = nd_gated_residual_bwd(dtype_id(dy), dy.data_ptr(), branch.data_ptr(), gate.data_ptr(), dbranch.data_ptr(),
+                               part.data_ptr<float>(), B * S, 0, S, H, kGatedTileRows, current_stream(dy));
+  }
+  check_status(st, "fused_gated_residual_backward");
+  return {dsum, dbranch, part.sum(1)};  // the tiles of a sample, summed in one fixed order
+}
+
+// AdaLN / AdaRMSNorm forward with FP8 e4m3 output under a caller-given scale (delayed scaling): -> [q, scale[B,H],
+// mean, invstd] / [q, scale[B,H], inv_rms]; `amax` (optional device float) receives max(amax, max |y|)
+std::vector<at::Tensor> norm_forward_e4m3(bool rms, const at::Tensor& x, const at::Tensor& scale, const at::Tensor& shift,
+                                          double eps, const at::Tensor& q_scale, c10::optional<at::Tensor> amax) {
+  check_norm_inputs(x, scale, shift);
+  TORCH_CHECK(q_scale.is_cuda() && q_scale.scalar_type() == at::kFloat && q_scale.numel() == 1 &&
+                  q_scale.device() == x.device(), "q_scale must be one float32 on x's device");
+  float* amax_p = nullptr;
+  if (amax.has_value() && amax->defined()) {
+    TORCH_CHECK(amax->is_cuda() && amax->scalar_type() == at::kFloat && amax->numel() == 1 && amax->device() == x.device(),
+                "amax must be one float32 on x's device");
+    amax_p = amax->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t B = x.size(0), S = x.size(1), H = x.size(2);
+  at::Tensor scale_c = scale.reshape({B, H}).contiguous(), shift_c = shift.reshape({B, H}).contiguous();
+  at::Tensor q = at::empty(x.sizes(), x.options().dtype(at::kFloat8_e4m3fn));
+  auto stat_opts = x.options().dtype(at::kFloat).requires_grad(false);
+  at::Tensor invstd = at::empty({B, S}, stat_opts), mean;
+  int st;
+  if (rms) {
+    st = nd_adarms_fwd_e4m3(dtype_id(x), x.data_ptr(), scale_c.data_ptr(), shift_c.data_ptr(), q.data_ptr(),
+                            invstd.data_ptr<float>(), q_scale.data_ptr<float>(), amax_p, B * S, 0, S, H,
+                            static_cast<float>(eps), current_stream(x));
+  } else {
+    mean = at::empty({B, S}, stat_opts);
+    st = nd_adaln_fwd_e4m3(dtype_id(x), x.data_ptr(), scale_c.data_ptr(), shift_c.data_ptr(), q.data_ptr(),
+                           mean.data_ptr<float>(), invstd.data_ptr<float>(), q_scale.data_ptr<float>(), amax_p, B * S, 0, S,
+                           H, static_cast<float>(eps), current_stream(x));
+  }
+  check_status(st, rms ? "fused_adarmsnorm_forward_e4m3" : "fused_adaln_forward_e4m3");
+  if (rms) return {q, scale_c, invstd};
+  return {q, scale_c, mean, invstd};
+}
+std::vector<at::Tensor> fused_adaln_forward_e4m3(const at::Tensor& x, const at::Tensor& scale, const at::Tensor& shift,
+                                                 double eps, const at::Tensor& q_scale, c10::optional<at::Tensor> amax) {
+  return norm_forward_e4m3(false, x, scale, shift, eps, q_scale, amax);
+}
+std::vector<at::Tensor> fused_adarmsnorm_forward_e4m3(const at::Tensor& x, const at::Tensor& scale, const at::Tensor& shift,
+                                                      double eps, const at::Tensor& q_scale, c10::optional<at::Tensor> amax) {
+  return norm_forward_e4m3(true, x, scale, shift, eps, q_scale, amax);
+}
+
+// per-tensor amax scaling to e4m3 on the device: -> [q, scale (one float32: amax / 448)]
+std::vector<at::Tensor> quantize_e4m3(const at::Tensor& x) {
+  ND_CHECK_INPUT(x);
+  TORCH_CHECK(dtype_id(x) >= 0, "quantize_e4m3 supports fp32/fp16/bf16 tensors");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto f32 = x.options().dtype(at::kFloat);
+  at::Tensor ws = at::empty({static_cast<int64_t>(nd_amax_ws_bytes())}, x.options().dtype(at::kByte));  // per call: no sharing across streams
+  at::Tensor amax = at::empty({1}, f32), scale = at::empty({1}, f32);
+  at::Tensor q = at::empty(x.sizes(), x.options().dtype(at::kFloat8_e4m3fn));
+  check_status(nd_amax(dtype_id(x), x.data_ptr(), x.numel(), amax.data_ptr<float>(), ws.data_ptr(), ws.numel(),
+                       current_stream(x)), "quantize_e4m3 (amax)");
+  check_status(nd_quant_e4m3(dtype_id(x), x.data_ptr(), x.numel(), amax.data_ptr<float>(), q.data_ptr(),
+                             scale.data_ptr<float>(), current_stream(x)), "quantize_e4m3");
+  return {q, scale};
+}
+
+// FC1 on e4m3 operands: x_q [B, S, H], w_q [N, H] (rows [gate | value] when gated), bias (16-bit, optional),
+// scales = two device floats (x's and w's de-quantisation scales) -> y in `out_bf16 ? bf16 : fp16`
+at::Tensor fused_fc1_bias_act_forward_fp8(const at::Tensor& x_q, const at::Tensor& w_q, c10::optional<at::Tensor> bias,
+                                          const at::Tensor& scales, int64_t act_id, bool gated, bool out_bf16) {
+  ND_CHECK_INPUT(x_q);
+  ND_CHECK_INPUT(w_q);
+  TORCH_CHECK(x_q.scalar_type() == at::kFloat8_e4m3fn && w_q.scalar_type() == at::kFloat8_e4m3fn, "x_q and w_q must be e4m3");
+  TORCH_CHECK(x_q.dim() == 3 && w_q.dim() == 2 && w_q.size(1) == x_q.size(2), "x_q [B, S, H] and w_q [N, H]");
+  TORCH_CHECK(!gated || w_q.size(0) % 2 == 0, "weight.size(0) must be even");
+  TORCH_CHECK(scales.is_cuda() && scales.scalar_type() == at::kFloat && scales.numel() == 2 && scales.is_contiguous() &&
+                  scales.device() == x_q.device(), "scales must be two float32 on x's device");
+  TORCH_CHECK(act_id == 0 || act_id == 1, "act_id must be 0 (SiLU) or 1 (GELU)");
+  const auto out_t = out_bf16 ? at::kBFloat16 : at::kHalf;
+  const void* bias_p = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_cuda() && bias->is_contiguous() && bias->numel() == w_q.size(0) && bias->scalar_type() == out_t,
+                "bias must be a contiguous CUDA tensor of weight.size(0) elements in the output dtype");
+    bias_p = bias->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(x_q.device());
+  const int64_t n = w_q.size(0), n_out = gated ? n / 2 : n;
+  at::Tensor y = at::empty({x_q.size(0), x_q.size(1), n_out}, x_q.options().dtype(out_t));
+  check_status(nd_fc1_fwd(ND_E4M3, out_bf16 ? ND_BF16 : ND_F16, static_cast<int>(act_id), gated ? 1 : 0, x_q.data_ptr(),
+                          w_q.data_ptr(), bias_p, 1.0f, scales.data_ptr<float>(), y.data_ptr(), x_q.size(0) * x_q.size(1),
+                          x_q.size(2), n, nullptr, current_stream(x_q)),
+               "fused_fc1_bias_act_forward_fp8");
+  return y;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("fused_residual_adaln_forward", &fused_residual_adaln_forward,
+        "x + gate * branch and its AdaLN in one pass -> [x_new, y, scale[B,H], mean, invstd]");
+  m.def("fused_residual_adarmsnorm_forward", &fused_residual_adarmsnorm_forward,
+        "x + gate * branch and its AdaRMSNorm in one pass -> [x_new, y, scale[B,H], inv_rms]");
+  m.def("fused_gated_residual_forward", &fused_gated_residual_forward, "y = x + gate[b] * branch");
+  m.def("fused_gated_residual_backward", &fused_gated_residual_backward,
+        "(dy [+ dres]) -> [dsum, dbranch, dgate[B,H] fp32]");
+  m.def("fused_adaln_forward_e4m3", &fused_adaln_forward_e4m3, "AdaLN forward with e4m3 output -> [q, scale, mean, invstd]");
+  m.def("fused_adarmsnorm_forward_e4m3", &fused_adarmsnorm_forward_e4m3, "AdaRMSNorm forward with e4m3 output -> [q, scale, inv_rms]");
+  m.def("quantize_e4m3", &quantize_e4m3, "per-tensor amax scaling to e4m3 -> [q, scale]");
+  m.def("fused_fc1_bias_act_forward_fp8", &fused_fc1_bias_act_forward_fp8, "FC1 + bias + activation on e4m3 operands");
   m.def("fused_adaln_forward", &fused_adaln_forward, "fused AdaLN forward -> [y, scale[B,H], mean, invstd]");
   m.def("fused_adaln_forward_inference", &fused_adaln_forward_inference, "fused AdaLN forward, y only");
   m.def("fused_adaln_backward_dx", &fused_adaln_backward_dx, "fused AdaLN backward dx");

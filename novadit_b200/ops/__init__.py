@@ -49,6 +49,7 @@ from .fc1_bias_act import (  # noqa: E402
     fc1_bias_act_ref,
     fused_fc1_bias_act,
     fused_fc1_bias_act_fp8,
+    quantize_e4m3,
     interleave_bias,
     interleave_weight,
     split_gated_weight,
@@ -61,8 +62,12 @@ from .qkv_pack import fused_qkv_linear_pack, fused_qkv_pack, qkv_pack_ref  # noq
 from .residual import (  # noqa: E402
     fused_gated_residual,
     fused_out_residual,
+    fused_residual_adaln,
+    fused_residual_adarmsnorm,
     gated_residual_ref,
     out_residual_ref,
+    residual_adaln_ref,
+    residual_adarmsnorm_ref,
 )
 
 __all__ = [
@@ -90,6 +95,11 @@ __all__ = [
     "un_interleave_bias",
     "split_gated_weight",
     "fused_gated_residual",
+    "fused_residual_adaln",
+    "fused_residual_adarmsnorm",
+    "residual_adaln_ref",
+    "residual_adarmsnorm_ref",
+    "quantize_e4m3",
     "fused_out_residual",
     "gated_residual_ref",
     "fused_qkv_linear_pack",

@@ -78,12 +78,8 @@ def fused_adaln_e4m3(x, scale, shift, eps: float, q_scale, amax=None):
     q = saturate_e4m3(y / q_scale) with the shape of x. `q_scale` is a 1-element fp32 CUDA tensor (delayed scaling:
     derived from an earlier step's maximum as amax / 448); `amax`, when given, is a 1-element fp32 CUDA tensor that
     receives max(amax, max |y|) of this call. No counterpart in the reference (it has no FP8 path)."""
-    from .. import capi
-
-    require_cuda_extension("fused_adaln_e4m3", x, "adaln_ref")
-    b = x.shape[0]
-    return capi.norm_fwd_e4m3("layer", x.contiguous(), scale.reshape(b, -1).contiguous(),
-                              shift.reshape(b, -1).contiguous(), eps, q_scale, amax, stats=False)[0]
+    ext = require_cuda_extension("fused_adaln_e4m3", x, "adaln_ref")
+    return ext.fused_adaln_forward_e4m3(x.contiguous(), scale.contiguous(), shift.contiguous(), eps, q_scale, amax)[0]
 
 
 def fused_adaln_backward_dx(dy, x, scale, mean, invstd):

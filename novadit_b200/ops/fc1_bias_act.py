@@ -106,12 +106,21 @@ def fused_fc1_bias_act_fp8(x, weight, bias=None, activation: str = "gelu", gated
     x and weight are quantised on the device (amax -> scale -> saturating e4m3), the GEMM runs
     in `kind::f8f6f4` with fp32 accumulation, and the two de-quantisation scales are applied in
     the epilogue before bias and activation. Pass `weight_q=(q, scale)` from an earlier
-    `capi.quantize_e4m3(weight)` to skip re-quantising a static weight. Returns bf16/fp16.
+    `quantize_e4m3(weight)` to skip re-quantising a static weight. x [B, S, H] (or [M, H]); returns bf16/fp16.
     """
-    from .. import capi
+    ext = require_cuda_extension("fused_fc1_bias_act_fp8", x, "fc1_bias_act_ref")
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("fused_fc1_bias_act_fp8 needs fp16 or bf16 activations (the output takes their dtype)")
+    x3 = x.contiguous() if x.dim() == 3 else x.contiguous().unsqueeze(0)
+    qx, sx = ext.quantize_e4m3(x3)
+    qw, sw = weight_q if weight_q is not None else ext.quantize_e4m3(weight.contiguous())
+    y = ext.fused_fc1_bias_act_forward_fp8(qx, qw, bias, torch.cat([sx, sw]), 0 if activation == "silu" else 1,
+                                           bool(gated), x.dtype == torch.bfloat16)
+    return y if x.dim() == 3 else y.squeeze(0)
 
-    require_cuda_extension("fused_fc1_bias_act_fp8", x, "fc1_bias_act_ref")
-    qx, sx = capi.quantize_e4m3(x.contiguous())
-    qw, sw = weight_q if weight_q is not None else capi.quantize_e4m3(weight.contiguous())
-    scales = torch.cat([sx, sw])
-    return capi.fc1_fwd(qx, qw, bias, activation, gated, alpha_dev=scales, out_dtype=x.dtype)
+
+@torch.no_grad()
+def quantize_e4m3(x):
+    """Per-tensor amax scaling to e4m3 on the device: (q, scale) with scale = amax / 448 as a 1-element fp32 tensor."""
+    ext = require_cuda_extension("quantize_e4m3", x, "torch.Tensor.to(torch.float8_e4m3fn)")
+    return tuple(ext.quantize_e4m3(x.contiguous()))
