@@ -412,6 +412,30 @@ def bench_extras(dev, stream, hbm_peak: float, tf_peak: float, tf_sustained: flo
     out["fp8_quantise_x_ms"] = time_graph_loop(g, 20, stream)
     del xf, wf, bf, qx, qw, y
 
+    # FC1 backward at the DiT-XL/2 MLP shape (M = 8192 tokens, H = 1152, 2I = 9216): the activation backward with
+    # recomputation (one tcgen05 launch), dx = dz W and dW = dz^T x on the tcgen05 GEMM that reads its operands in
+    # place, dbias; each next to the library call the reference's backward makes for it
+    mt, hh, n2 = 8192, 1152, 9216
+    xb_, wb_, bb_ = (t.to(dev) for t in synth.fc1_inputs(mt, hh, n2, torch.bfloat16, seed=1))
+    dyb = torch.randn(mt, n2 // 2, device=dev).to(torch.bfloat16)
+    dzb = capi.fc1_bwd_dz(xb_, wb_, bb_, dyb, "gelu", status=status)
+    gf = 2.0 * mt * hh * n2
+    ms = time_graph_loop(capture(lambda: capi.fc1_bwd_dz(xb_, wb_, bb_, dyb, "gelu", status=status)), 20, stream)
+    out["fc1_bwd_dz_recompute"] = {"TFLOP/s": gf / ms / 1e9, "ms": ms}
+    for name, fn, lib in (("dx", lambda: capi.fc1_bwd_gemm(dzb, wb_, "dx", status=status), lambda: dzb @ wb_),
+                          ("dw", lambda: capi.fc1_bwd_gemm(dzb, xb_, "dw", status=status), lambda: dzb.t() @ xb_)):
+        fn()
+        lib()
+        ms = time_graph_loop(capture(fn), 20, stream)
+        ms_lib = time_graph_loop(capture(lib), 20, stream)
+        out[f"fc1_bwd_{name}"] = {"TFLOP/s": gf / ms / 1e9, "ms": ms, "frac_of_bf16_peak": gf / ms / 1e9 / tf_peak,
+                                  "library_gemm_ms": ms_lib, "speedup_vs_library": ms_lib / ms}
+    capi.colsum(dzb)
+    ms = time_graph_loop(capture(lambda: capi.colsum(dzb)), 20, stream)
+    ms_lib = time_graph_loop(capture(lambda: dzb.sum(dim=0)), 20, stream)
+    out["fc1_bwd_dbias"] = {"ms": ms, "GB/s": mt * n2 * 2 / ms / 1e6, "library_sum_ms": ms_lib}
+    del xb_, wb_, bb_, dyb, dzb
+
     # FC1, the large case of workload config 4: M=32768, K=3072, N=12288 (2.47 TFLOP per launch, ~2 ms: a kernel
     # this long runs under the power cap, so its fraction is taken of the SUSTAINED bf16 figure)
     m, k, n = 32768, 3072, 12288

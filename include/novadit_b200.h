@@ -268,6 +268,25 @@ int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const void* x, c
 int nd_fc1_bwd_dz(int dtype, int act, const void* x, const void* w, const void* bias, const void* dy,
                   void* dz, int64_t m, int64_t k, int64_t n, int* status, void* stream);
 
+/* The two GEMMs of the FC1 backward on the tcgen05 path, fp32 accumulation, operands read where they lie (UMMA
+ * takes W and, for dW, dz as MN-major operands: no transpose copy per call, unlike the reference's
+ * _backward_dx_cute, novadit/ops/fc1_bias_act.py:309-315, which copies and transposes both weight halves):
+ *   op 0: c [m, n] = a [m, k] @ b [k, n]       dx = dz @ W    (m tokens, k = 2I, n = H): the job of
+ *         FC1GatedActSM120BF16BackwardDxKernel, csrc/cute_dsl/fc1_bias_act/fc1_bias_act.py:996-1913
+ *   op 1: c [m, n] = a [k, m]^T @ b [k, n]     dW = dz^T @ x  (m = 2I, k tokens, n = H): replaces the
+ *         `dz_flat.T @ x_flat` of novadit/ops/fc1_bias_act.py:276
+ * fp16 / bf16, all three matrices row-major and dense; n (and k for op 0, m for op 1) a multiple of 8, bases
+ * 16-byte aligned, else ND_ERR_UNSUPPORTED. 128 x 192 tiles. `status` as in nd_fc1_fwd. */
+int nd_fc1_bwd_gemm(int dtype, int op, const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                    int* status, void* stream);
+
+/* out [cols] = column sums of x [rows, cols] (fp16 / bf16, cols a multiple of 8) with fp32 accumulation in a fixed
+ * order (two stages through `ws`, nd_colsum_ws_bytes(cols) bytes, 16-byte aligned): dbias = sum of dz over the
+ * tokens, the `dz_flat.sum(dim=0)` of novadit/ops/fc1_bias_act.py:279. */
+size_t nd_colsum_ws_bytes(int64_t cols);
+int nd_colsum(int dtype, const void* x, int64_t rows, int64_t cols, void* out, void* ws, size_t ws_bytes,
+              void* stream);
+
 /* amax = max |x| over n elements (fp32 result, device). Two-stage and deterministic:
  * `ws` holds per-CTA maxima; nd_amax_ws_bytes() bytes, 256-byte aligned. No counterpart in
  * the reference (it has no FP8 path). */

@@ -28,6 +28,12 @@ void nd_tune_norm_stages(int stages);
 void nd_tune_norm_pdl(int enabled);
 /* Tuning hook: cap on CTAs per SM of the bulk-copy norm kernels (0 = what occupancy allows). */
 void nd_tune_norm_chunks_per_sm(int n);
+/* Test hook for the abort path of the bulk-copy norm kernels. `limit_ns` bounds every wait on a bulk copy (0
+ * restores the default of one second); with `withhold_first_copy` != 0 CTA 0 never sends its first copy, so its
+ * first wait expires with nothing in flight: the kernel sets the device error word (nd_device_error: 1 forward,
+ * 2 backward), the CTA leaves through the abort path and the launch completes; the context stays usable and the
+ * launch's output is incomplete. Process-wide; tests reset both. */
+void nd_tune_norm_wait_test(unsigned long long limit_ns, int withhold_first_copy);
 /* Tuning hook for the gate-act kernels: rows per CTA group (1, 2 or 4; 0 = default) and 1 = a single
  * resident wave of CTAs striding over the groups instead of one CTA per group (default 0). Process-wide.
  * No counterpart in the reference. */

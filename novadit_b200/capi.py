@@ -34,6 +34,7 @@ SIGNATURES = {
     "nd_tune_norm_stages": (None, [c_int]),
     "nd_tune_norm_pdl": (None, [c_int]),
     "nd_tune_norm_chunks_per_sm": (None, [c_int]),
+    "nd_tune_norm_wait_test": (None, [ctypes.c_uint64, c_int]),
     "nd_adaln_fwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              *_SHAPE4, c_float, c_void_p]),
     "nd_adaln_bwd_dx": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -80,6 +81,9 @@ SIGNATURES = {
                            c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "nd_fc1_bwd_dz": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                               c_int64, c_void_p, c_void_p]),
+    "nd_fc1_bwd_gemm": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "nd_colsum_ws_bytes": (c_size_t, [c_int64]),
+    "nd_colsum": (c_int, [c_int, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
     "nd_tune_gate_act": (None, [c_int, c_int]),
     "nd_tune_fc1_pair": (None, [c_int]),
     "nd_tune_fc1_trace": (None, [c_void_p]),
@@ -403,6 +407,31 @@ def fc1_bwd_dz(x, w, bias, dy, act="silu", status=None):
     check(lib().nd_fc1_bwd_dz(DTYPE_IDS[x.dtype], ACT_IDS[act], _ptr(x), _ptr(w), _ptr(bias), _ptr(dy), _ptr(dz),
                               m, k, n, _ptr(status), _stream()), "nd_fc1_bwd_dz")
     return dz
+
+
+def fc1_bwd_gemm(a, b, op: str, status=None):
+    """op "dx": a [m, k] @ b [k, n]; op "dw": a [k, m]^T @ b [k, n]. Returns c [m, n] in a's dtype."""
+    _need_cuda(a, b, status)
+    if op == "dx":
+        m, k = a.shape
+    else:
+        k, m = a.shape
+    n = b.shape[1]
+    c = torch.empty(m, n, dtype=a.dtype, device=a.device)
+    check(lib().nd_fc1_bwd_gemm(DTYPE_IDS[a.dtype], 0 if op == "dx" else 1, _ptr(a), _ptr(b), _ptr(c), m, n, k,
+                                _ptr(status), _stream()), "nd_fc1_bwd_gemm")
+    return c
+
+
+def colsum(x):
+    """Column sums of a [rows, cols] fp16 / bf16 matrix (fp32 accumulation, fixed order), in x's dtype."""
+    _need_cuda(x)
+    rows, cols = x.shape
+    L = lib()
+    ws = torch.empty(L.nd_colsum_ws_bytes(cols), dtype=torch.uint8, device=x.device)
+    out = torch.empty(cols, dtype=x.dtype, device=x.device)
+    check(L.nd_colsum(DTYPE_IDS[x.dtype], _ptr(x), rows, cols, _ptr(out), _ptr(ws), ws.numel(), _stream()), "nd_colsum")
+    return out
 
 
 _AMAX_WS: dict = {}

@@ -823,6 +823,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn encode_fn() {
+  // cuTensorMapEncodeTiled is a driver call and wants a CUDA context current on the calling thread. A thread that
+  // has only used cached runtime state so far (PyTorch's autograd worker calling a backward entry point first) may
+  // have none bound yet: one runtime call that needs the context binds the device's primary context to the thread.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    (void)cudaFree(nullptr);
+    context_bound = true;
+  }
   static EncodeTiledFn fn = nullptr;
   static std::once_flag once;
   std::call_once(once, [] {
@@ -881,6 +889,284 @@ static const void* pick_fc1_pair(int act, int gated) {
 
 static std::atomic<int> g_fc1_pair{-1};  // -1 = choose per problem
 static std::atomic<long long*> g_fc1_trace{nullptr};
+
+
+// ------------------------------------------------------------------ the two GEMMs of the FC1 backward
+// dx = dz W   (dz [M, 2I], W [2I, H]: the reduction runs over 2I, W's rows)         A K-major,  B MN-major
+// dW = dz^T x (dz [M, 2I], x [M, H]:  the reduction runs over the M token rows)      A MN-major, B MN-major
+// In both the B operand - and for dW the A operand too - is contiguous along its M/N dimension, not along K. UMMA
+// takes such operands in place ("MN-major", instruction-descriptor bits 15 / 16), so nothing is transposed or
+// copied. An MN-major tile is staged as boxes of 64 elements (128 bytes, along M/N) x 64 K-rows with the 128-byte
+// swizzle: K-row r of a box sits at r * 128 bytes, 8-row groups are 1024 bytes apart (the descriptor's stride
+// offset), boxes 8192 bytes apart (its leading offset), and one UMMA of K = 16 consumes two 8-row groups, so the
+// k-th slice of a stage starts 2048 k bytes into it.
+// Tiles are 128 x 192: H = 1152 is six of them exactly (a 256-wide tile wastes 10 % there), 192 fp32 columns
+// twice fit tensor memory, and a CTA reads 10 KB of operands per MMA of 96 cycles, within what shared memory
+// delivers. One CTA per SM, persistent over tiles; warp 0 copies, warp 1 issues, warps 2-5 drain one 32-row
+// quarter of the accumulator each (no bias, no activation: the epilogue is a rounding).
+constexpr int kGemmBN = 192;
+constexpr int kGemmStages = 5;
+constexpr int kGemmBoxBytes = 64 * 128;                       // one MN-major box: 64 K-rows of 128 bytes
+constexpr int kGemmBBytes = (kGemmBN / 64) * kGemmBoxBytes;   // 24 KB
+constexpr int kGemmStageBytes = kATileBytes + kGemmBBytes;    // 40 KB
+constexpr int kGemmThreads = 64 + 4 * 32;
+
+struct __align__(1024) GemmSmem {
+  uint8_t stage[kGemmStages][kGemmStageBytes];
+  uint8_t out[4][kOutBlockBytes];
+  uint64_t full[kGemmStages];
+  uint64_t empty[kGemmStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct GemmArgs {
+  Fc1Sink sink;
+  int m, n, k;
+  int tiles_m, tiles_n, k_blocks;
+};
+
+// MN-major, 128B-swizzled operand tile (see above): leading offset 8192 bytes, stride offset 1024 bytes
+__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(kGemmBoxBytes >> 4) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+__host__ __device__ constexpr uint32_t umma_idesc_gemm(uint32_t ab_format, bool a_mn) {
+  return (1u << 4) | (ab_format << 7) | (ab_format << 10) | (a_mn ? (1u << 15) : 0u) | (1u << 16) |
+         ((kGemmBN >> 3) << 17) | ((kBM >> 4) << 24);
+}
+
+template <int ABF, bool A_MN, typename OUT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_c, const GemmArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  GemmSmem& s = *reinterpret_cast<GemmSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &s.abort_flag;
+  const int total_tiles = a.tiles_m * a.tiles_n;
+  auto coords = [&](int t, int& mi, int& ni) {  // groups of 8 row tiles share their B tiles in L2
+    const int per_group = kGroupM * a.tiles_n;
+    const int g = t / per_group, first_m = g * kGroupM;
+    const int gm = (a.tiles_m - first_m) < kGroupM ? (a.tiles_m - first_m) : kGroupM;
+    const int r = t - g * per_group;
+    mi = first_m + r % gm;
+    ni = r / gm;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kGemmStages; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.tmem_full[i], 1);
+      mbar_init(&s.tmem_empty[i], 4);
+    }
+    s.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s.tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---------------------------------------------------------- copies
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int mi, ni;
+        coords(t, mi, ni);
+        const int m0 = mi * kBM, n0 = ni * kGemmBN;
+        for (int kb = 0; kb < a.k_blocks; ++kb) {
+          ok = mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag, a.sink, 21);
+          if (!ok) break;
+          mbar_expect_tx(&s.full[stage], kGemmStageBytes);
+          uint8_t* base = s.stage[stage];
+          if constexpr (A_MN) {
+            tma_load_2d(base, &map_a, &s.full[stage], m0, kb * 64);
+            tma_load_2d(base + kGemmBoxBytes, &map_a, &s.full[stage], m0 + 64, kb * 64);
+          } else {
+            tma_load_2d(base, &map_a, &s.full[stage], kb * 64, m0);
+          }
+#pragma unroll
+          for (int j = 0; j < kGemmBN / 64; ++j)
+            tma_load_2d(base + kATileBytes + j * kGemmBoxBytes, &map_b, &s.full[stage], n0 + 64 * j, kb * 64);
+          if (++stage == kGemmStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {  // let copies already issued land in shared memory before the CTA may exit
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {  // ---------------------------------------------------------- MMA issue
+      const int my_tiles = static_cast<int>(blockIdx.x) < total_tiles
+                               ? (total_tiles - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1 : 0;
+      constexpr uint32_t idesc = umma_idesc_gemm(ABF, A_MN);
+      const uint32_t stage0 = smem_u32(s.stage[0]);
+      const uint64_t a_d0 = A_MN ? umma_desc_mn(stage0) : umma_desc(stage0);
+      const uint64_t b_d0 = umma_desc_mn(stage0 + kATileBytes);
+      const uint32_t a_hi = static_cast<uint32_t>(a_d0 >> 32), b_hi = static_cast<uint32_t>(b_d0 >> 32);
+      const uint32_t a_lo0 = static_cast<uint32_t>(a_d0), b_lo0 = static_cast<uint32_t>(b_d0);
+      constexpr uint32_t a_step = A_MN ? (2048u >> 4) : 2u;  // one K = 16 slice further, in 16-byte address units
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int i = 0; i < my_tiles && ok; ++i) {
+        ok = mbar_wait(&s.tmem_empty[acc], acc_phase ^ 1u, abort_flag, a.sink, 22);
+        if (!ok) break;
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 256);
+        for (int kb = 0; kb < a.k_blocks; ++kb) {
+          ok = mbar_wait(&s.full[stage], phase, abort_flag, a.sink, 23);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t so = static_cast<uint32_t>(stage) * (kGemmStageBytes >> 4);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t al = a_lo0 + so + a_step * kk, bl = b_lo0 + so + (2048u >> 4) * kk;
+            const uint32_t accum = (kb != 0 || kk != 0) ? 1u : 0u;
+            asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tmov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %6};\n\t"
+                         "setp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+                         ::"r"(d_tmem), "r"(al), "r"(bl), "r"(idesc), "r"(accum), "r"(a_hi), "r"(b_hi)
+                         : "memory");
+          }
+          tc_commit_to<false>(&s.empty[stage]);
+          if (++stage == kGemmStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit_to<false>(&s.tmem_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------------ epilogue: 4 warps, 32 rows each
+    const int q = warp & 3;
+    uint8_t* obuf = s.out[warp - 2];
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int mi, ni;
+      coords(t, mi, ni);
+      ok = __all_sync(0xffffffffu, mbar_wait(&s.tmem_full[acc], acc_phase, abort_flag, a.sink, 24));
+      if (!ok) break;
+      tc_fence_after();
+      const int row0 = mi * kBM + q * 32;
+      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * 256);
+#pragma unroll 1
+      for (int ch = 0; ch < kGemmBN / 32; ++ch) {
+        float z[32];
+        tc_ld32(t_lane + ch * 32, z);
+        tc_wait_ld();
+        if (lane == 0) bulk_wait_read_all();  // the previous block has left the staging memory
+        __syncwarp();
+        const int sw = (lane >> 1) & 3;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 pk;
+          pk.x = pack2<OUT>(z[c * 8 + 0], z[c * 8 + 1]);
+          pk.y = pack2<OUT>(z[c * 8 + 2], z[c * 8 + 3]);
+          pk.z = pack2<OUT>(z[c * 8 + 4], z[c * 8 + 5]);
+          pk.w = pack2<OUT>(z[c * 8 + 6], z[c * 8 + 7]);
+          *reinterpret_cast<uint4*>(obuf + lane * 64 + ((c ^ sw) << 4)) = pk;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        const int col = ni * kGemmBN + ch * 32;
+        if (lane == 0 && row0 < a.m && col < a.n) {
+          tma_store_2d(&map_c, obuf, col, row0);
+          bulk_commit();
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.tmem_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (lane == 0) bulk_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// `inner` contiguous elements x `outer` rows of a 16-bit matrix as boxes of 64 x 64 with the 128-byte swizzle
+static bool make_map_mn(CUtensorMap* map, CUtensorMapDataType dt, const void* base, long long inner, long long outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(inner) * 2};
+  const cuuint32_t box[2] = {64u, 64u}, estr[2] = {1u, 1u};
+  return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Column sums of a [rows, cols] 16-bit matrix in fp32, two stages, fixed order (dbias = sum of dz over the tokens).
+constexpr int kColsumChunks = 64;
+template <typename T>
+__global__ void __launch_bounds__(128) colsum_stage1(const T* __restrict__ x, float* __restrict__ part, long long rows,
+                                                     int cols) {
+  // thread -> 8 columns (one 16-byte vector); blockIdx.y -> chunk of rows
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v * 8 >= cols) return;
+  const long long per = (rows + kColsumChunks - 1) / kColsumChunks;
+  const long long r0 = blockIdx.y * per, r1 = r0 + per < rows ? r0 + per : rows;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (long long r = r0; r < r1; ++r) {
+    Vec<T, 8> w;
+    w.load_stream(x + r * cols + v * 8);
+    float f[8];
+    w.unpack(f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += f[i];
+  }
+  float* dst = part + static_cast<long long>(blockIdx.y) * cols + v * 8;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dst[i] = acc[i];
+}
+template <typename T>
+__global__ void __launch_bounds__(256) colsum_stage2(const float* __restrict__ part, T* __restrict__ out, int cols) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float acc = 0.f;
+#pragma unroll 8
+  for (int k = 0; k < kColsumChunks; ++k) acc += part[static_cast<long long>(k) * cols + c];  // chunks in order
+  out[c] = from_f32<T>(acc);
+}
 
 }  // namespace nd
 
@@ -1083,4 +1369,95 @@ extern "C" int nd_fc1_bwd_dz(int dtype, int act, const void* x, const void* w, c
     return ND_ERR_LAUNCH;
   }
   return ND_OK;
+}
+
+// The two GEMMs of the FC1 backward on the tcgen05 path, operands read where they lie (no transposes):
+//   op 0: c [m, n] = a [m, k] @ b [k, n]      (dx = dz @ W:   m tokens, k = 2I, n = H)
+//   op 1: c [m, n] = a [k, m]^T @ b [k, n]    (dW = dz^T @ x: m = 2I, k tokens, n = H)
+extern "C" int nd_fc1_bwd_gemm(int dtype, int op, const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                               int* status, void* stream) {
+  using namespace nd;
+  if (m < 0 || n <= 0 || k <= 0) return ND_ERR_BAD_ARG;
+  if (dtype != ND_BF16 && dtype != ND_F16) return ND_ERR_UNSUPPORTED;
+  if (op != 0 && op != 1) return ND_ERR_BAD_ARG;
+  if (m == 0) return ND_OK;
+  if (!a || !b || !c) return ND_ERR_BAD_ARG;
+  // row pitches of every tensor the copy engine walks must be multiples of 16 bytes
+  if (n % 8 != 0 || (op == 0 ? k % 8 != 0 : m % 8 != 0)) return ND_ERR_UNSUPPORTED;
+  if (!aligned16(a) || !aligned16(b) || !aligned16(c)) return ND_ERR_UNSUPPORTED;
+  if (m > INT32_MAX - kBM || n > INT32_MAX - kGemmBN || k > INT32_MAX - 256) return ND_ERR_UNSUPPORTED;
+  GemmArgs g{};
+  g.sink = Fc1Sink{status, device_error_ptr()};
+  g.m = static_cast<int>(m); g.n = static_cast<int>(n); g.k = static_cast<int>(k);
+  g.tiles_m = static_cast<int>((m + kBM - 1) / kBM);
+  g.tiles_n = static_cast<int>((n + kGemmBN - 1) / kGemmBN);
+  g.k_blocks = static_cast<int>((k + 63) / 64);
+  const long long tiles = static_cast<long long>(g.tiles_m) * g.tiles_n;
+  if (tiles > INT32_MAX) return ND_ERR_UNSUPPORTED;
+  const CUtensorMapDataType dt = dtype == ND_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap map_a, map_b, map_c;
+  const bool ok_a = op == 0 ? make_map(&map_a, dt, 2, a, m, k) : make_map_mn(&map_a, dt, a, m, k);
+  if (!ok_a || !make_map_mn(&map_b, dt, b, n, k)) return ND_ERR_LAUNCH;
+  {
+    EncodeTiledFn enc = encode_fn();
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(m)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(n) * 2};
+    const cuuint32_t box[2] = {32u, 32u}, estr[2] = {1u, 1u};
+    if (enc == nullptr ||
+        enc(&map_c, dt, 2, c, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return ND_ERR_LAUNCH;
+  }
+  const void* fn;
+  if (dtype == ND_BF16)
+    fn = op == 0 ? (const void*)gemm_bwd_kernel<1, false, __nv_bfloat16> : (const void*)gemm_bwd_kernel<1, true, __nv_bfloat16>;
+  else
+    fn = op == 0 ? (const void*)gemm_bwd_kernel<0, false, __half> : (const void*)gemm_bwd_kernel<0, true, __half>;
+  const int smem_bytes = static_cast<int>(sizeof(GemmSmem)) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    (void)cudaGetLastError();
+    return ND_ERR_LAUNCH;
+  }
+  void* params[] = {&map_a, &map_b, &map_c, &g};
+  cudaLaunchConfig_t cfg{};
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles < sm_count() ? tiles : sm_count()));
+  e = cudaLaunchKernelExC(&cfg, fn, params);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e);
+    (void)cudaGetLastError();
+    return ND_ERR_LAUNCH;
+  }
+  return ND_OK;
+}
+
+extern "C" size_t nd_colsum_ws_bytes(int64_t cols) {
+  return cols > 0 ? static_cast<size_t>(nd::kColsumChunks) * cols * sizeof(float) : 0;
+}
+
+// out [cols] = column sums of x [rows, cols] (16-bit; cols a multiple of 8), fp32 accumulation in a fixed order
+extern "C" int nd_colsum(int dtype, const void* x, int64_t rows, int64_t cols, void* out, void* ws, size_t ws_bytes,
+                         void* stream) {
+  using namespace nd;
+  if (rows < 0 || cols <= 0) return ND_ERR_BAD_ARG;
+  if (dtype != ND_BF16 && dtype != ND_F16) return ND_ERR_UNSUPPORTED;
+  if (cols % 8 != 0 || cols > INT32_MAX || !aligned16(x)) return ND_ERR_UNSUPPORTED;
+  if (!x || !out) return ND_ERR_BAD_ARG;
+  if (!ws || ws_bytes < nd_colsum_ws_bytes(cols) || (reinterpret_cast<uintptr_t>(ws) & 15u)) return ND_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const dim3 g1(static_cast<unsigned>((cols / 8 + 127) / 128), kColsumChunks);
+  const unsigned g2 = static_cast<unsigned>((cols + 255) / 256);
+  float* part = static_cast<float*>(ws);
+  if (dtype == ND_BF16) {
+    colsum_stage1<__nv_bfloat16><<<g1, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), part, rows, static_cast<int>(cols));
+    colsum_stage2<__nv_bfloat16><<<g2, 256, 0, st>>>(part, static_cast<__nv_bfloat16*>(out), static_cast<int>(cols));
+  } else {
+    colsum_stage1<__half><<<g1, 128, 0, st>>>(static_cast<const __half*>(x), part, rows, static_cast<int>(cols));
+    colsum_stage2<__half><<<g2, 256, 0, st>>>(part, static_cast<__half*>(out), static_cast<int>(cols));
+  }
+  return check_launch();
 }

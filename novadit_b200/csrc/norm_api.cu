@@ -18,6 +18,10 @@ static std::atomic<int> g_norm_cps{0};
 int norm_chunks_per_sm() { return g_norm_cps.load(std::memory_order_relaxed); }
 static std::atomic<int> g_norm_pdl{1};
 int norm_pdl_enabled() { return g_norm_pdl.load(std::memory_order_relaxed); }
+static std::atomic<unsigned long long> g_norm_wait_limit_ns{1000000000ull};
+unsigned long long norm_wait_limit_ns() { return g_norm_wait_limit_ns.load(std::memory_order_relaxed); }
+static std::atomic<int> g_norm_withhold{0};
+int norm_withhold_first_copy() { return g_norm_withhold.load(std::memory_order_relaxed); }
 int tile_rows_override() { return g_tile_rows_override.load(std::memory_order_relaxed); }
 int norm_variant() { return g_norm_variant.load(std::memory_order_relaxed); }
 
@@ -217,6 +221,13 @@ void nd_tune_norm_variant(int variant) { g_norm_variant.store(variant); }
 void nd_tune_norm_stages(int stages) { g_norm_stages.store(stages < 0 ? 0 : stages); }
 // Tuning hook: 0 launches the norm kernels without programmatic stream serialization (default 1).
 void nd_tune_norm_pdl(int enabled) { g_norm_pdl.store(enabled != 0); }
+// Test hook for the abort path of the bulk-copy norm kernels: `limit_ns` bounds every wait on a copy (0 restores
+// the 1 s default); `withhold_first_copy` != 0 makes CTA 0 leave its first copy unsent, so that its first wait
+// runs out with nothing in flight, the device error word is set and the CTA returns through the abort path.
+void nd_tune_norm_wait_test(unsigned long long limit_ns, int withhold_first_copy) {
+  g_norm_wait_limit_ns.store(limit_ns == 0 ? 1000000000ull : limit_ns);
+  g_norm_withhold.store(withhold_first_copy != 0);
+}
 // Tuning hook: cap on CTAs per SM of the bulk-copy norm kernels (0 = what occupancy allows).
 void nd_tune_norm_chunks_per_sm(int n) { g_norm_cps.store(n < 0 ? 0 : n); }
 

@@ -59,6 +59,10 @@ struct NormArgs {
   // and normalised; `dy` holds branch, `gate` the [B, H] gate (null: plain x + branch), `res` switches it on
   const void* gate;
   bool res;
+  // bounded waits of the bulk-copy kernels: the limit (1 s unless a test shortens it) and a test switch that makes
+  // CTA 0 leave its first copy unsent, so that its first wait runs out with nothing in flight
+  unsigned long long wait_limit_ns;
+  int withhold_first_copy;
 };
 
 // first row (local to the shard) of chunk c

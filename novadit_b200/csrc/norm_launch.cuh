@@ -15,6 +15,8 @@ namespace nd {
 
 int norm_stages_override();  // tuning: pipeline depth of the bulk-copy kernels (0 = by budget)
 
+unsigned long long norm_wait_limit_ns();  // tuning / test: limit of the bounded waits (default 1 s)
+int norm_withhold_first_copy();           // test: CTA 0 of the bulk-copy kernels leaves its first copy unsent
 int norm_pdl_enabled();      // tuning: launch with programmatic stream serialization (default on)
 int norm_chunks_per_sm();    // tuning: cap on CTAs per SM for the bulk-copy kernels (0 = occupancy)
 
@@ -209,6 +211,8 @@ int launch_norm(NormArgs a, cudaStream_t st) {
   const void* ptrs[] = {a.x, a.scale, a.shift, a.y, a.dy, a.dx, a.dscale, a.dshift, a.ws_part, a.gate};
   for (const void* p : ptrs) vec_ok = vec_ok && aligned16(p);
   a.err = device_error_ptr();
+  a.wait_limit_ns = norm_wait_limit_ns();
+  a.withhold_first_copy = norm_withhold_first_copy();
   // the residual in front of the norm exists in the bulk-copy kernels only: the caller composes the two operators
   if (a.res && (!vec_ok || a.hidden / VMAX > 512 || norm_variant() == 1)) return ND_ERR_UNSUPPORTED;
   if (!vec_ok) return a.q_scale != nullptr ? ND_ERR_UNSUPPORTED : launch_norm_generic<T, 1>(a, st);

@@ -60,14 +60,15 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// Wait on an mbarrier phase for at most one second. Returns false (and records `code` in the
-// device error word `err`, read on the host with nd_device_error()) on expiry.
-__device__ __forceinline__ bool mbar_wait_1s(uint64_t* bar, uint32_t parity, int* err, int code) {
+// Wait on an mbarrier phase for at most one second (`limit_ns`: a test may shorten it). Returns false (and
+// records `code` in the device error word `err`, read on the host with nd_device_error()) on expiry.
+__device__ __forceinline__ bool mbar_wait_1s(uint64_t* bar, uint32_t parity, int* err, int code,
+                                             unsigned long long limit_ns = 1000000000ull) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   for (uint32_t polls = 1;; ++polls) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((polls & 1023u) == 0 && global_ns() - t0 > 1000000000ull) {
+    if ((polls & 1023u) == 0 && global_ns() - t0 > limit_ns) {
       if (err != nullptr) atomicCAS(err, 0, code);
       return false;
     }

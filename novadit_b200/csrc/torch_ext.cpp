@@ -365,9 +365,9 @@ at::Tensor fused_fc1_bias_act_backward_dz(const at::Tensor& x, const at::Tensor&
 }
 
 // dx = dz @ weight for dz [B, S, 2I] and the FC1 weight [2I, H]: the job of the reference's CuTe-DSL backward-dx
-// kernel (csrc/cute_dsl/fc1_bias_act/fc1_bias_act.py:996-1913 behind novadit/ops/fc1_bias_act.py:288-326), run on
-// the tcgen05 GEMM of this library: the reduction runs over 2I, so the B operand is W^T [H, 2I], made K-major by
-// one transpose copy per call (the reference copies and transposes both weight halves per call, :309-315).
+// kernel (csrc/cute_dsl/fc1_bias_act/fc1_bias_act.py:996-1913 behind novadit/ops/fc1_bias_act.py:288-326), on the
+// tcgen05 GEMM that reads the weight in place as an MN-major operand (the reference copies and transposes both
+// weight halves per call, :309-315).
 at::Tensor fused_fc1_bias_act_backward_dx(const at::Tensor& dz, const at::Tensor& weight) {
   TORCH_CHECK(dz.is_cuda() && weight.is_cuda(), "dz and weight must be CUDA tensors");
   TORCH_CHECK(dz.dim() == 3, "dz must have shape [batch, seq, 2 * intermediate]");
@@ -376,14 +376,45 @@ at::Tensor fused_fc1_bias_act_backward_dx(const at::Tensor& dz, const at::Tensor
   TORCH_CHECK(dz.scalar_type() == at::kHalf || dz.scalar_type() == at::kBFloat16,
               "fused_fc1_bias_act_backward_dx supports fp16 and bf16 inputs");
   c10::cuda::CUDAGuard guard(dz.device());
-  at::Tensor dzc = dz.contiguous();
-  at::Tensor wt = weight.t().contiguous();  // [H, 2I], reduction dimension contiguous
+  at::Tensor dzc = dz.contiguous(), wc = weight.contiguous();
   at::Tensor dx = at::empty({dz.size(0), dz.size(1), weight.size(1)}, dz.options());
-  check_status(nd_fc1_fwd(dtype_id(dz), dtype_id(dz), ND_ACT_NONE, /*gated=*/0, dzc.data_ptr(), wt.data_ptr(), nullptr,
-                          1.0f, nullptr, dx.data_ptr(), dz.size(0) * dz.size(1), dz.size(2), weight.size(1), nullptr,
-                          current_stream(dz)),
+  check_status(nd_fc1_bwd_gemm(dtype_id(dz), 0, dzc.data_ptr(), wc.data_ptr(), dx.data_ptr(), dz.size(0) * dz.size(1),
+                               weight.size(1), dz.size(2), nullptr, current_stream(dz)),
                "fused_fc1_bias_act_backward_dx");
   return dx;
+}
+
+// dW [2I, H] = dz^T @ x for dz [B, S, 2I] and x [B, S, H] (novadit/ops/fc1_bias_act.py:276), both read in place
+at::Tensor fused_fc1_bias_act_backward_dw(const at::Tensor& dz, const at::Tensor& x) {
+  TORCH_CHECK(dz.is_cuda() && x.is_cuda(), "dz and x must be CUDA tensors");
+  TORCH_CHECK(dz.dim() == 3 && x.dim() == 3 && dz.size(0) == x.size(0) && dz.size(1) == x.size(1),
+              "dz [batch, seq, 2 * intermediate] and x [batch, seq, hidden]");
+  TORCH_CHECK(dz.scalar_type() == x.scalar_type(), "dz and x must have the same dtype");
+  TORCH_CHECK(dz.scalar_type() == at::kHalf || dz.scalar_type() == at::kBFloat16,
+              "fused_fc1_bias_act_backward_dw supports fp16 and bf16 inputs");
+  c10::cuda::CUDAGuard guard(dz.device());
+  at::Tensor dzc = dz.contiguous(), xc = x.contiguous();
+  at::Tensor dw = at::empty({dz.size(2), x.size(2)}, dz.options());
+  check_status(nd_fc1_bwd_gemm(dtype_id(dz), 1, dzc.data_ptr(), xc.data_ptr(), dw.data_ptr(), dz.size(2), x.size(2),
+                               dz.size(0) * dz.size(1), nullptr, current_stream(dz)),
+               "fused_fc1_bias_act_backward_dw");
+  return dw;
+}
+
+// dbias [2I] = sum of dz [B, S, 2I] over batch and sequence (novadit/ops/fc1_bias_act.py:279), fp32 accumulation
+at::Tensor fused_fc1_bias_act_backward_dbias(const at::Tensor& dz) {
+  TORCH_CHECK(dz.is_cuda() && dz.dim() == 3, "dz must be a CUDA tensor of shape [batch, seq, 2 * intermediate]");
+  TORCH_CHECK(dz.scalar_type() == at::kHalf || dz.scalar_type() == at::kBFloat16,
+              "fused_fc1_bias_act_backward_dbias supports fp16 and bf16 inputs");
+  c10::cuda::CUDAGuard guard(dz.device());
+  at::Tensor dzc = dz.contiguous();
+  const int64_t cols = dz.size(2);
+  at::Tensor ws = at::empty({static_cast<int64_t>(nd_colsum_ws_bytes(cols))}, dz.options().dtype(at::kByte));
+  at::Tensor out = at::empty({cols}, dz.options());
+  check_status(nd_colsum(dtype_id(dz), dzc.data_ptr(), dz.size(0) * dz.size(1), cols, out.data_ptr(), ws.data_ptr(),
+                         ws.numel(), current_stream(dz)),
+               "fused_fc1_bias_act_backward_dbias");
+  return out;
 }
 
 // ------------------------------------------------------------------ row operators next to the path
@@ -642,6 +673,8 @@ at::Tensor fused_fc1_bias_act_forward_fp8(const at::Tensor& x_q, const at::Tenso
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("fused_fc1_bias_act_backward_dw", &fused_fc1_bias_act_backward_dw, "dW [2I, H] = dz^T @ x on the tcgen05 path");
+  m.def("fused_fc1_bias_act_backward_dbias", &fused_fc1_bias_act_backward_dbias, "dbias [2I] = sum of dz over the tokens");
   m.def("fused_residual_adaln_forward", &fused_residual_adaln_forward,
         "x + gate * branch and its AdaLN in one pass -> [x_new, y, scale[B,H], mean, invstd]");
   m.def("fused_residual_adarmsnorm_forward", &fused_residual_adarmsnorm_forward,

@@ -75,12 +75,16 @@ class _FusedFc1BiasActFunction(torch.autograd.Function):
         else:
             z = F.linear(x, weight, bias)  # recomputed, as in the reference
             dz = ext.fused_gate_act_backward_gate_first(dy.contiguous(), z, ctx.act_id)  # one pass, not ~8 eager ones
+        if hidden % 8 == 0 and inter % 4 == 0:
+            # dx = dz W and dW = dz^T x on the tcgen05 GEMM that reads W, dz and x in place (MN-major operands, 128 x
+            # 192 tiles), dbias by the two-stage column sum: no library GEMM or reduction in the backward pass
+            dx = ext.fused_fc1_bias_act_backward_dx(dz, weight) if ctx.needs_input_grad[0] else None
+            d_w = ext.fused_fc1_bias_act_backward_dw(dz, x) if ctx.needs_input_grad[1] else None
+            d_b = ext.fused_fc1_bias_act_backward_dbias(dz) if bias is not None and ctx.needs_input_grad[2] else None
+            return dx, d_w, d_b, None
+        # rows the copy engine cannot walk (pitches that are not multiples of 16 bytes): PyTorch's GEMMs
         m = x.shape[0] * x.shape[1]
         dz_flat, x_flat = dz.reshape(m, -1), x.reshape(m, -1)
-        # dx = dz W: a plain GEMM. `novadit_cuda.fused_fc1_bias_act_backward_dx` runs it on this library's tcgen05
-        # kernel (W^T made K-major by a transpose copy, as the reference's backward-dx kernel does), but at the
-        # DiT-XL/2 shape (M 8192, reduction 9216, 1152 outputs) its 256-wide tiles leave the last of three rounds
-        # 16 % full: 154 us + 48 us for the transpose against 123 us for the library GEMM, which is used here.
         dx = (dz_flat @ weight).reshape(x.shape)
         d_w = dz_flat.T @ x_flat
         d_b = dz_flat.sum(dim=0) if bias is not None else None

@@ -223,6 +223,65 @@ def test_unsupported_shapes_are_rejected_not_mangled():
                         y.data_ptr(), 8, 16, 8, None, st) == -2
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k", [
+    (256, 192, 128),      # exactly one row of tiles, two k-blocks
+    (304, 264, 520),      # ragged in all three dimensions (row tile, column tile and k-block hang over)
+    (1024, 1152, 2304),   # H = 1152: six column tiles, reduction over 2I = 2304
+    (128, 64, 64),        # a single tile narrower than one box row
+])
+def test_backward_gemms_read_their_operands_in_place(dtype, m, n, k):
+    """nd_fc1_bwd_gemm: op "dx" = a [m, k] @ b [k, n] (b MN-major), op "dw" = a [k, m]^T @ b [k, n] (both MN-major),
+    against the fp64 products of the same 16-bit inputs."""
+    gen = torch.Generator().manual_seed(m + n + k)
+    a = (torch.randn(m, k, generator=gen) * 0.5).to(dtype)
+    at = (torch.randn(k, m, generator=gen) * 0.5).to(dtype)
+    b = (torch.randn(k, n, generator=gen) * 0.5).to(dtype)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got = capi.fc1_bwd_gemm(a.to(DEV), b.to(DEV), "dx", status=status)
+    want = a.double() @ b.double()
+    assert_half_parity_scaled(got.cpu(), want, f"dx gemm {dtype} {(m, n, k)}")
+    got = capi.fc1_bwd_gemm(at.to(DEV), b.to(DEV), "dw", status=status)
+    want = at.double().T @ b.double()
+    assert_half_parity_scaled(got.cpu(), want, f"dw gemm {dtype} {(m, n, k)}")
+    assert int(status.item()) == 0
+
+
+def assert_half_parity_scaled(got, want64, what):
+    """A GEMM output has no O(1) scale: compare relative to the result's rms (rel-L2 <= 1e-2 of the bar set, and no
+    element further than 2e-2 rms-units + one rounding step from the fp64 value)."""
+    rms = float(want64.pow(2).mean().sqrt())
+    assert oracle.rel_l2(got.double(), want64) <= 1e-2, what
+    step = torch.finfo(got.dtype).eps * want64.abs().clamp_min(rms)
+    assert bool(((got.double() - want64).abs() <= 2e-2 * rms + step).all()), what
+
+
+def test_backward_dw_and_dbias_bindings_and_the_autograd_function():
+    gen = torch.Generator().manual_seed(21)
+    b, s, h, inter = 2, 200, 264, 256
+    x = torch.randn(b, s, h, generator=gen).to(DEV, torch.bfloat16)
+    w = (torch.randn(2 * inter, h, generator=gen) * 0.05).to(DEV, torch.bfloat16)
+    bias = (torch.randn(2 * inter, generator=gen) * 0.05).to(DEV, torch.bfloat16)
+    dz = torch.randn(b, s, 2 * inter, generator=gen).to(DEV, torch.bfloat16)
+    ext = ops.novadit_cuda
+    dw = ext.fused_fc1_bias_act_backward_dw(dz, x)
+    want = dz.double().reshape(-1, 2 * inter).T @ x.double().reshape(-1, h)
+    assert dw.shape == (2 * inter, h)
+    assert_half_parity_scaled(dw.cpu(), want.cpu(), "backward dW")
+    db = ext.fused_fc1_bias_act_backward_dbias(dz)
+    assert_half_parity_scaled(db.cpu(), dz.double().sum(dim=(0, 1)).cpu(), "backward dbias")
+    # the whole Function: gradients of <y, dy> against the fp32 PyTorch definition on the same bf16 values
+    dy = torch.randn(b, s, inter, generator=gen).to(DEV, torch.bfloat16)
+    leaves = [t.clone().requires_grad_(True) for t in (x, w, bias)]
+    y = ops.fused_fc1_bias_act(*leaves, "gelu")
+    grads = torch.autograd.grad(y, leaves, dy)
+    ref_leaves = [t.float().requires_grad_(True) for t in (x, w, bias)]
+    yr = ops.fc1_bias_act_ref(*ref_leaves, "gelu")
+    ref_grads = torch.autograd.grad(yr, ref_leaves, dy.float())
+    for g, r, name in zip(grads, ref_grads, ("dx", "dW", "dbias")):
+        assert oracle.rel_l2(g.float().cpu(), r.cpu()) < 1e-2, name
+
+
 def test_fc1_launches_leave_the_device_error_word_clear():
     """The FC1 kernels record an expired wait in the device error word (codes 101..) as well as in the caller's
     status word, so that launches through the torch extension, which passes no status word, are covered by

@@ -384,3 +384,31 @@ def test_full_size_properties(kind):
         wdx = oracle.adarms_bwd(dys, xs, sc, 1e-6, compute=torch.float64)[0]
     assert_half_parity(y.reshape(-1, h)[rows].cpu().unsqueeze(1), wy, "sampled rows y")
     assert_half_parity(dx.reshape(-1, h)[rows].cpu().unsqueeze(1), wdx, "sampled rows dx")
+
+
+def test_an_expired_wait_sets_the_error_word_and_the_launch_returns():
+    """The abort path of the bulk-copy norm kernels, exercised without faulting or hanging anything: the wait limit
+    is shortened to 2 ms and CTA 0 is told not to send its first copy (nothing is in flight for that stage), so its
+    first wait runs out. The kernel must record the expiry in the device error word, leave through the abort path
+    and complete; afterwards the context is usable and an ordinary launch gives the ordinary result."""
+    L = capi.lib()
+    x, scale, shift, dy = (t.to(DEV) for t in synth.norm_inputs(4, 64, 1152, torch.bfloat16, seed=5))
+    want_y, mean, invstd = capi.norm_fwd("layer", x, scale, shift, 1e-6)
+    want_dx, want_ds, want_dh = capi.norm_bwd("layer", dy, x, scale, mean, invstd)
+    torch.cuda.synchronize()
+    assert L.nd_device_error(1) == 0
+    try:
+        L.nd_tune_norm_wait_test(2_000_000, 1)
+        capi.norm_fwd("layer", x, scale, shift, 1e-6)
+        torch.cuda.synchronize()                      # the launch completes: no hang, no fault
+        assert L.nd_device_error(1) == 1              # forward wait expired (and the word is cleared again)
+        capi.norm_bwd("layer", dy, x, scale, mean, invstd)
+        torch.cuda.synchronize()
+        assert L.nd_device_error(1) == 2              # backward wait expired
+    finally:
+        L.nd_tune_norm_wait_test(0, 0)
+    y, _, _ = capi.norm_fwd("layer", x, scale, shift, 1e-6)
+    dx, ds, dh = capi.norm_bwd("layer", dy, x, scale, mean, invstd)
+    torch.cuda.synchronize()
+    assert L.nd_device_error(0) == 0
+    assert torch.equal(y, want_y) and torch.equal(dx, want_dx) and torch.equal(ds, want_ds) and torch.equal(dh, want_dh)
