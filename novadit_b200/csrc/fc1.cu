@@ -222,12 +222,15 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 // the block to the copy engine. A thread writing its own row straight to global memory costs the L1 one tag
 // lookup per row and instruction (32 per store instruction), which made the stores the longest part of the
 // epilogue; the bulk store writes whole 64-byte row segments and costs the warp one instruction.
-template <int GATED, int ACT, typename OUT>
+template <int GATED, int ACT, typename OUT, bool FAST = false>
 __device__ __forceinline__ void epilogue_columns(const Fc1Args& a, const CUtensorMap* map_y, const float* sb,
                                                  uint8_t* obuf, uint32_t t_lane, int row0, int ni, int colhalf,
                                                  float alpha, int lane) {
   const int out0 = GATED != 0 ? ni * 128 : ni * kBN;  // first output column of the tile
   constexpr int kSteps = GATED != 0 ? 4 : 8;          // steps of 32 output columns per tile
+  // FAST (FP8 operands): one special-function instruction per activation; two of them per output are what bounds
+  // this epilogue (16 per clock and SM against 128 x 128 outputs per tile), next to an MMA stream twice as fast
+  auto actf = [](float g) { return FAST ? act_fwd_fast<ACT>(g) : act_fwd<ACT>(g); };
   // bias values come from shared memory four at a time (all lanes read the same address)
   const float4* sb4 = reinterpret_cast<const float4*>(sb);
 #pragma unroll 1
@@ -245,7 +248,7 @@ __device__ __forceinline__ void epilogue_columns(const Fc1Args& a, const CUtenso
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int j = j4 * 4 + e;
-          out[j] = fmaf(v[j], alpha, bvs[e]) * act_fwd<ACT>(fmaf(g[j], alpha, bgs[e]));
+          out[j] = fmaf(v[j], alpha, bvs[e]) * actf(fmaf(g[j], alpha, bgs[e]));
         }
       }
     } else if constexpr (GATED == 2) {
@@ -256,10 +259,10 @@ __device__ __forceinline__ void epilogue_columns(const Fc1Args& a, const CUtenso
 #pragma unroll
       for (int j4 = 0; j4 < 8; ++j4) {
         const float4 b0 = sb4[ch * 16 + j4], b1 = sb4[ch * 16 + 8 + j4];
-        out[2 * j4] = fmaf(z0[4 * j4 + 1], alpha, b0.y) * act_fwd<ACT>(fmaf(z0[4 * j4], alpha, b0.x));
-        out[2 * j4 + 1] = fmaf(z0[4 * j4 + 3], alpha, b0.w) * act_fwd<ACT>(fmaf(z0[4 * j4 + 2], alpha, b0.z));
-        out[16 + 2 * j4] = fmaf(z1[4 * j4 + 1], alpha, b1.y) * act_fwd<ACT>(fmaf(z1[4 * j4], alpha, b1.x));
-        out[16 + 2 * j4 + 1] = fmaf(z1[4 * j4 + 3], alpha, b1.w) * act_fwd<ACT>(fmaf(z1[4 * j4 + 2], alpha, b1.z));
+        out[2 * j4] = fmaf(z0[4 * j4 + 1], alpha, b0.y) * actf(fmaf(z0[4 * j4], alpha, b0.x));
+        out[2 * j4 + 1] = fmaf(z0[4 * j4 + 3], alpha, b0.w) * actf(fmaf(z0[4 * j4 + 2], alpha, b0.z));
+        out[16 + 2 * j4] = fmaf(z1[4 * j4 + 1], alpha, b1.y) * actf(fmaf(z1[4 * j4], alpha, b1.x));
+        out[16 + 2 * j4 + 1] = fmaf(z1[4 * j4 + 3], alpha, b1.w) * actf(fmaf(z1[4 * j4 + 2], alpha, b1.z));
       }
     } else {
       float z[32];
@@ -268,10 +271,10 @@ __device__ __forceinline__ void epilogue_columns(const Fc1Args& a, const CUtenso
 #pragma unroll
       for (int j4 = 0; j4 < 8; ++j4) {
         const float4 b = sb4[ch * 8 + j4];
-        out[4 * j4 + 0] = act_fwd<ACT>(fmaf(z[4 * j4 + 0], alpha, b.x));
-        out[4 * j4 + 1] = act_fwd<ACT>(fmaf(z[4 * j4 + 1], alpha, b.y));
-        out[4 * j4 + 2] = act_fwd<ACT>(fmaf(z[4 * j4 + 2], alpha, b.z));
-        out[4 * j4 + 3] = act_fwd<ACT>(fmaf(z[4 * j4 + 3], alpha, b.w));
+        out[4 * j4 + 0] = actf(fmaf(z[4 * j4 + 0], alpha, b.x));
+        out[4 * j4 + 1] = actf(fmaf(z[4 * j4 + 1], alpha, b.y));
+        out[4 * j4 + 2] = actf(fmaf(z[4 * j4 + 2], alpha, b.z));
+        out[4 * j4 + 3] = actf(fmaf(z[4 * j4 + 3], alpha, b.w));
       }
     }
     if (lane == 0) bulk_wait_read_all();  // the previous block has left the staging memory
@@ -592,7 +595,7 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
                                        abort_flag, t_lane, row0, ni, colhalf, alpha, lane, ok);
         if (!ok) break;
       } else {
-        epilogue_columns<GATED, ACT, OUT>(a, &map_y, sb, s.out[warp - 2][0], t_lane, row0, ni, colhalf, alpha, lane);
+        epilogue_columns<GATED, ACT, OUT, F8>(a, &map_y, sb, s.out[warp - 2][0], t_lane, row0, ni, colhalf, alpha, lane);
       }
       tc_fence_before();
       __syncwarp();
@@ -798,7 +801,7 @@ fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       tc_fence_after();
       const int row0 = mi * 2 * kBM + static_cast<int>(rank) * kBM + q * 32;
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * kBN);
-      epilogue_columns<GATED, ACT, OUT>(a, &map_y, sb, s.out[warp - 2], t_lane, row0, ni, colhalf, alpha, lane);
+      epilogue_columns<GATED, ACT, OUT, F8>(a, &map_y, sb, s.out[warp - 2], t_lane, row0, ni, colhalf, alpha, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&s.tmem_empty[acc]), 0));  // the leader counts both CTAs
