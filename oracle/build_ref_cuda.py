@@ -10,7 +10,7 @@ system and copies no source. The reference's kernels use `cutlass::AlignedArray`
 (the variable the reference's setup.py reads) or, failing that, from the CUTLASS headers that the installed
 `flashinfer` package carries. Without either the build raises. The module is named `novadit_cuda_ref` so that it can be imported next to this
 repository's `novadit_cuda`. Used by tests/test_gpu_reference_cuda.py (parity of this library against the
-reference's kernels on the same GPU) and oracle/compare_ref_cuda.py (their speed, side by side).
+reference's kernels on the same GPU).
 """
 from __future__ import annotations
 
