@@ -428,7 +428,13 @@ def bench_extras(dev, stream, hbm_peak: float, tf_peak: float, tf_sustained: flo
         lib()
         ms = time_graph_loop(capture(fn), 20, stream)
         ms_lib = time_graph_loop(capture(lib), 20, stream)
+        # the same GEMM on whole 128 x 192 single-CTA tiles (what a call without a workspace runs)
+        whole = (lambda nm: lambda: capi.fc1_bwd_gemm(dzb, wb_ if nm == "dx" else xb_, nm, status=status,
+                                                      workspace=False))(name)
+        whole()
+        ms_whole = time_graph_loop(capture(whole), 20, stream)
         out[f"fc1_bwd_{name}"] = {"TFLOP/s": gf / ms / 1e9, "ms": ms, "frac_of_bf16_peak": gf / ms / 1e9 / tf_peak,
+                                  "whole_single_cta_tiles_ms": ms_whole,
                                   "library_gemm_ms": ms_lib, "speedup_vs_library": ms_lib / ms}
     capi.colsum(dzb)
     ms = time_graph_loop(capture(lambda: capi.colsum(dzb)), 20, stream)

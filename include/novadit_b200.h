@@ -276,9 +276,16 @@ int nd_fc1_bwd_dz(int dtype, int act, const void* x, const void* w, const void* 
  *   op 1: c [m, n] = a [k, m]^T @ b [k, n]     dW = dz^T @ x  (m = 2I, k tokens, n = H): replaces the
  *         `dz_flat.T @ x_flat` of novadit/ops/fc1_bias_act.py:276
  * fp16 / bf16, all three matrices row-major and dense; n (and k for op 0, m for op 1) a multiple of 8, bases
- * 16-byte aligned, else ND_ERR_UNSUPPORTED. 128 x 192 tiles. `status` as in nd_fc1_fwd. */
+ * 16-byte aligned, else ND_ERR_UNSUPPORTED. `status` as in nd_fc1_fwd.
+ * `ws` (nd_fc1_bwd_gemm_ws_bytes() bytes, 256-byte aligned, no initialisation needed, may be shared by launches
+ * on one stream) lets the launch cut the reduction dimension evenly over the GPU: 256 x 256 tiles on CTA pairs
+ * (tcgen05 cta_group::2), the k-blocks of all tiles laid end to end and shared out in equal ranges, a tile cut
+ * between two pairs finished by whichever of the two comes second from fp32 partials in `ws`; the result does not
+ * depend on which. With ws == NULL (or too small) the launch falls back to whole 128 x 192 tiles per CTA, which
+ * leaves the last round of tiles partly empty at DiT shapes. */
+size_t nd_fc1_bwd_gemm_ws_bytes(void);
 int nd_fc1_bwd_gemm(int dtype, int op, const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
-                    int* status, void* stream);
+                    void* ws, size_t ws_bytes, int* status, void* stream);
 
 /* out [cols] = column sums of x [rows, cols] (fp16 / bf16, cols a multiple of 8) with fp32 accumulation in a fixed
  * order (two stages through `ws`, nd_colsum_ws_bytes(cols) bytes, 16-byte aligned): dbias = sum of dz over the

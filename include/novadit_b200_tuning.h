@@ -41,10 +41,16 @@ void nd_tune_gate_act(int rows_per_group, int persistent);
 /* Tuning hook: 1 = two-CTA tiles (tcgen05 cta_group::2 over clusters of two CTAs), 0 = single-CTA
  * tiles, negative (default) = chosen per problem. Process-wide. No counterpart in the reference. */
 void nd_tune_fc1_pair(int mode);
+/* The same choice for the backward GEMMs (nd_fc1_bwd_gemm) when a workspace is given: 1 = 256 x 256 tiles over CTA
+ * pairs with the k-blocks shared out evenly, 0 = whole 128 x 192 single-CTA tiles, negative (default) = chosen per
+ * problem. Process-wide. No counterpart in the reference. */
+void nd_tune_fc1_bwd_pair(int mode);
 /* Diagnostic hook: a device array of 8 int64 that later nd_fc1_fwd launches add cycle counters to
  * ([0] copy thread waiting for a free stage, [3]/[4] one epilogue warp waiting / working, [5]/[7] the
- * copy thread's lifetime in cycles / nanoseconds); NULL (default) turns it off. No counterpart in the
- * reference. */
+ * copy thread's lifetime in cycles / nanoseconds); NULL (default) turns it off. The CTA-pair launches of
+ * nd_fc1_bwd_gemm add, per cluster, the issuing thread's [0] cycles waiting for a drained accumulator, [1]
+ * cycles waiting for operands, [5] lifetime in cycles, [6] one, [7] its number of k-blocks. No counterpart in
+ * the reference. */
 void nd_tune_fc1_trace(long long* device_counters);
 
 #ifdef __cplusplus

@@ -81,11 +81,14 @@ SIGNATURES = {
                            c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "nd_fc1_bwd_dz": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                               c_int64, c_void_p, c_void_p]),
-    "nd_fc1_bwd_gemm": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "nd_fc1_bwd_gemm_ws_bytes": (c_size_t, []),
+    "nd_fc1_bwd_gemm": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_size_t,
+                                c_void_p, c_void_p]),
     "nd_colsum_ws_bytes": (c_size_t, [c_int64]),
     "nd_colsum": (c_int, [c_int, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
     "nd_tune_gate_act": (None, [c_int, c_int]),
     "nd_tune_fc1_pair": (None, [c_int]),
+    "nd_tune_fc1_bwd_pair": (None, [c_int]),
     "nd_tune_fc1_trace": (None, [c_void_p]),
     "nd_amax_ws_bytes": (c_size_t, []),
     "nd_amax": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
@@ -409,8 +412,12 @@ def fc1_bwd_dz(x, w, bias, dy, act="silu", status=None):
     return dz
 
 
-def fc1_bwd_gemm(a, b, op: str, status=None):
-    """op "dx": a [m, k] @ b [k, n]; op "dw": a [k, m]^T @ b [k, n]. Returns c [m, n] in a's dtype."""
+_GEMM_WS: dict = {}
+
+
+def fc1_bwd_gemm(a, b, op: str, status=None, workspace=True):
+    """op "dx": a [m, k] @ b [k, n]; op "dw": a [k, m]^T @ b [k, n]. Returns c [m, n] in a's dtype.
+    `workspace=False` passes no workspace (whole single-CTA tiles instead of evenly cut CTA-pair tiles)."""
     _need_cuda(a, b, status)
     if op == "dx":
         m, k = a.shape
@@ -418,8 +425,16 @@ def fc1_bwd_gemm(a, b, op: str, status=None):
         k, m = a.shape
     n = b.shape[1]
     c = torch.empty(m, n, dtype=a.dtype, device=a.device)
-    check(lib().nd_fc1_bwd_gemm(DTYPE_IDS[a.dtype], 0 if op == "dx" else 1, _ptr(a), _ptr(b), _ptr(c), m, n, k,
-                                _ptr(status), _stream()), "nd_fc1_bwd_gemm")
+    L = lib()
+    st = _stream()
+    ws = None
+    if workspace:
+        key = (a.device, st or 0)  # per device AND stream: launches on two streams must not share partial tiles
+        ws = _GEMM_WS.get(key)
+        if ws is None:
+            ws = _GEMM_WS[key] = torch.empty(L.nd_fc1_bwd_gemm_ws_bytes(), dtype=torch.uint8, device=a.device)
+    check(L.nd_fc1_bwd_gemm(DTYPE_IDS[a.dtype], 0 if op == "dx" else 1, _ptr(a), _ptr(b), _ptr(c), m, n, k,
+                            _ptr(ws), ws.numel() if ws is not None else 0, _ptr(status), st), "nd_fc1_bwd_gemm")
     return c
 
 

@@ -1127,6 +1127,376 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   }
 }
 
+// ------------------------------------------------------------------ the same GEMMs over CTA pairs, K split evenly
+// What the tensor pipe charges for an MMA here does not depend on N: measured with a free-running issue loop, an
+// MMA of K = 16 takes ~160 cycles on a single CTA (M = 128) and ~128 cycles on a CTA pair (M = 256, 128 rows per
+// CTA), whether N is 128, 192 or 256 - the rows stream through, the columns lie side by side. So the cost of a GEMM
+// is its NUMBER of MMAs, a 128 x 192 tile uses 60 % of the pipe at best, and the efficient shape is the pair's
+// 256 x 256 tile. H = 1152 is four and a half of those: a row block costs five tiles' worth of MMAs (the half tile
+// is charged like a full one), and 160 or 180 tiles of 144 or 128 k-blocks do not divide over 74 clusters. Hence
+// the k-blocks of all tiles are laid end to end and cut into one contiguous range per cluster, equal to within one
+// k-block ("stream-K"). A range is at least one tile long, so a tile is cut at most once: the two clusters that
+// share it each write their fp32 partial accumulator to the caller's workspace and count themselves in, per warp
+// quarter; whoever comes second adds the two (a sum of two is the same in either order, so the result does not
+// depend on who that is) and writes the tile. Nobody waits for anybody.
+// Each CTA stages ITS 128 rows of A and ITS half of the tile's B columns, the leader's one thread issues the MMAs
+// over both CTAs' shared memory, and each CTA drains its own 128 lanes of tensor memory.
+constexpr int kGpStages = 6;
+constexpr int kGpBHalfBytes = 2 * kGemmBoxBytes;             // a CTA's half of a 256-wide B tile: two boxes, 16 KB
+constexpr int kGpStageBytes = kATileBytes + kGpBHalfBytes;   // 32 KB
+constexpr int kGpCounterBytes = 4096;                        // head of the workspace: arrival counters
+constexpr size_t kGpPartialFloats = 128 * 256;               // one CTA's share of a partial tile
+
+struct __align__(1024) GemmPairSmem {
+  uint8_t stage[kGpStages][kGpStageBytes];
+  uint8_t out[4][kOutBlockBytes];
+  uint64_t full[kGpStages];    // used in the leader only: counts the bytes of both CTAs
+  uint64_t empty[kGpStages];   // in each CTA: signalled by the leader's commits (multicast to the pair)
+  uint64_t tmem_full[2];       // in each CTA, likewise
+  uint64_t tmem_empty[2];      // used in the leader only: the epilogue warps of both CTAs arrive here
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct GemmPairArgs {
+  Fc1Sink sink;
+  long long* trace;   // nullable: cycle counters of the leader's issuing thread (see nd_tune_fc1_trace)
+  int* counters;      // zeroed before the launch; [boundary][rank][quarter]
+  float* partials;    // [boundary][side][rank][quarter][chunk][float4 index][lane][4]
+  long long total_it; // tiles x k-blocks
+  int m, n, k;
+  int tiles_n, k_blocks;
+};
+
+// The segments (tile, k-block range) of one cluster's share, in the order every role of both CTAs walks them: the
+// cut tile at the END of the range first, then the cut tile at its beginning, then the whole tiles in between. Both
+// halves of a shared tile are then computed early by their two clusters, and the second one's finishing pass over
+// the partials runs under the MMAs of the tiles that follow instead of at the end of the kernel.
+struct SegWalk {
+  long long g0, g1, g;   // the range, and the next whole-tile position
+  int kbs, tiles_n, step;
+  __device__ __forceinline__ SegWalk(const GemmPairArgs& a, int cluster, int clusters)
+      : kbs(a.k_blocks), tiles_n(a.tiles_n), step(0) {
+    const long long base = a.total_it / clusters, rem = a.total_it % clusters;
+    g0 = cluster * base + (cluster < rem ? cluster : rem);
+    g1 = g0 + base + (cluster < rem ? 1 : 0);
+    g = g0;
+  }
+  __device__ __forceinline__ long long length() const { return g1 - g0; }
+  __device__ __forceinline__ void tile_of(long long t, int& row_block, int& col_tile) const {
+    row_block = static_cast<int>(t / tiles_n);
+    col_tile = static_cast<int>(t - static_cast<long long>(row_block) * tiles_n);
+  }
+  // the tile cut by the end of the range (continued by the next cluster); `take` removes it from the range
+  __device__ __forceinline__ int tail_len() const {
+    const long long t = g1 / kbs;
+    const int tail = static_cast<int>(g1 - t * kbs);
+    return (tail != 0 && t * kbs >= g0) ? tail : 0;  // (a range inside one tile cannot occur: a range is >= a tile)
+  }
+  // the tile cut by the beginning of the range (begun by the previous cluster)
+  __device__ __forceinline__ int head_len() const {
+    const long long t = g0 / kbs;
+    const int off = static_cast<int>(g0 - t * kbs);
+    return off != 0 ? kbs - off : 0;
+  }
+  __device__ __forceinline__ bool next(int& row_block, int& col_tile, int& kb0, int& kb1) {
+    // steps 0 and 1: the two cut tiles, the SHORTER one first - its epilogue (store the partial, maybe finish the
+    // tile) then runs under the longer one's MMAs and has freed its accumulator when the first whole tile wants it
+    while (step < 2) {
+      const int tail = tail_len(), head = head_len();
+      const bool tail_turn = (step == 0) == (tail <= head);
+      ++step;
+      if (tail_turn && tail != 0) {
+        tile_of(g1 / kbs, row_block, col_tile);
+        kb0 = 0;
+        kb1 = tail;
+        return true;
+      }
+      if (!tail_turn && head != 0) {
+        tile_of(g0 / kbs, row_block, col_tile);
+        kb0 = kbs - head;
+        kb1 = kbs;
+        return true;
+      }
+    }
+    if (step == 2) {  // the whole tiles in between
+      step = 3;
+      g = g0 + head_len();
+      g1 -= tail_len();
+    }
+    if (g >= g1) return false;
+    tile_of(g / kbs, row_block, col_tile);
+    kb0 = 0;
+    kb1 = kbs;
+    g += kbs;
+    return true;
+  }
+};
+
+__host__ __device__ constexpr uint32_t umma_idesc_gemm_pair(uint32_t ab_format, bool a_mn, uint32_t n) {
+  return (1u << 4) | (ab_format << 7) | (ab_format << 10) | (a_mn ? (1u << 15) : 0u) | (1u << 16) | ((n >> 3) << 17) |
+         ((256u >> 4) << 24);
+}
+
+template <int ABF, bool A_MN, typename OUT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bwd_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const __grid_constant__ CUtensorMap map_c, const GemmPairArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  GemmPairSmem& s = *reinterpret_cast<GemmPairSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &s.abort_flag;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int cluster = static_cast<int>(cluster_id_x()), clusters = static_cast<int>(cluster_count_x());
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kGpStages; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.tmem_full[i], 1);
+      mbar_init(&s.tmem_empty[i], 2 * 4);
+    }
+    s.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s.tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything is signalled across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = s.tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---------------------------------------------------------- copies (one thread in each CTA)
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      SegWalk walk(a, cluster, clusters);
+      int rb, ct, kb0, kb1;
+      while (ok && walk.next(rb, ct, kb0, kb1)) {
+        const int wide = (a.n - ct * 256) > 128 ? 1 : 0;                  // the last column tile may be a half tile
+        const int m0 = rb * 2 * kBM + static_cast<int>(rank) * kBM;       // this CTA's 128 rows of the tile
+        const int n0 = ct * 256 + static_cast<int>(rank) * (wide ? 128 : 64);  // this CTA's half of the columns
+        const uint32_t both = 2u * static_cast<uint32_t>(kATileBytes + (wide ? 2 : 1) * kGemmBoxBytes);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = mbar_wait(&s.empty[stage], phase ^ 1u, abort_flag, a.sink, 31);
+          if (!ok) break;
+          if (rank == 0) mbar_expect_tx(&s.full[stage], both);
+          const uint32_t leader_full = mapa_u32(smem_u32(&s.full[stage]), 0);
+          uint8_t* base = s.stage[stage];
+          if constexpr (A_MN) {
+            tma_load_2d_pair(base, &map_a, leader_full, m0, kb * 64);
+            tma_load_2d_pair(base + kGemmBoxBytes, &map_a, leader_full, m0 + 64, kb * 64);
+          } else {
+            tma_load_2d_pair(base, &map_a, leader_full, kb * 64, m0);
+          }
+          tma_load_2d_pair(base + kATileBytes, &map_b, leader_full, n0, kb * 64);
+          if (wide) tma_load_2d_pair(base + kATileBytes + kGemmBoxBytes, &map_b, leader_full, n0 + 64, kb * 64);
+          if (++stage == kGpStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {  // let copies already issued land in shared memory before the CTA may exit
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {  // ---------------------------------------------- MMA issue (the leader's thread)
+      // The tensor pipe takes only a shallow queue of MMAs: the barrier of the NEXT stage is polled before the
+      // current stage's MMAs are issued, and the stage ring is unrolled so that addresses fold to constants.
+      const long long t_start = a.trace != nullptr ? clock64() : 0;
+      const uint32_t stage0 = smem_u32(s.stage[0]);
+      const uint64_t a_d0 = A_MN ? umma_desc_mn(stage0) : umma_desc(stage0);
+      const uint64_t b_d0 = umma_desc_mn(stage0 + kATileBytes);
+      const uint32_t a_hi = static_cast<uint32_t>(a_d0 >> 32), b_hi = static_cast<uint32_t>(b_d0 >> 32);
+      const uint32_t a_lo0 = static_cast<uint32_t>(a_d0), b_lo0 = static_cast<uint32_t>(b_d0);
+      constexpr uint32_t a_step = A_MN ? (2048u >> 4) : 2u;  // one K = 16 slice further, in 16-byte address units
+      constexpr uint32_t b_step = 2048u >> 4;
+      long long waited_full = 0, waited_acc = 0;
+      long long* trf = a.trace != nullptr ? &waited_full : nullptr;
+      long long* tra = a.trace != nullptr ? &waited_acc : nullptr;
+      SegWalk walk(a, cluster, clusters);
+      const long long total_it = walk.length();
+      int rb, ct, kb = 0, kb0 = 0, kb1 = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0, idesc = 0, d_tmem = 0;
+      bool ok = true;
+      bool ready = total_it > 0 && mbar_try_wait(&s.full[0], 0);
+      for (long long it0 = 0; it0 < total_it && ok; it0 += kGpStages) {
+#pragma unroll
+        for (int st = 0; st < kGpStages; ++st) {
+          if (it0 + st >= total_it) break;
+          if (kb == kb1) {  // a new segment: its accumulator must have been drained by the epilogues
+            walk.next(rb, ct, kb0, kb1);
+            kb = kb0;
+            idesc = umma_idesc_gemm_pair(ABF, A_MN, (a.n - ct * 256) > 128 ? 256u : 128u);
+            d_tmem = tmem_base + static_cast<uint32_t>(acc * 256);
+            ok = mbar_wait_timed(&s.tmem_empty[acc], acc_phase ^ 1u, abort_flag, a.sink, 32, tra);
+            if (!ok) break;
+          }
+          if (!ready) {
+            ok = mbar_wait_timed(&s.full[st], phase, abort_flag, a.sink, 33, trf);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          const int nst = (st + 1) % kGpStages;  // the ring is unrolled: st and nst fold to constants
+          ready = (it0 + st + 1 < total_it) && mbar_try_wait(&s.full[nst], st + 1 == kGpStages ? phase ^ 1u : phase);
+          const uint32_t so = static_cast<uint32_t>(st) * (kGpStageBytes >> 4);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t al = a_lo0 + so + a_step * kk, bl = b_lo0 + so + b_step * kk;
+            const uint32_t accum = (kb != kb0 || kk != 0) ? 1u : 0u;
+            asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tmov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %6};\n\t"
+                         "setp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %3, p;\n\t}"
+                         ::"r"(d_tmem), "r"(al), "r"(bl), "r"(idesc), "r"(accum), "r"(a_hi), "r"(b_hi)
+                         : "memory");
+          }
+          tc_commit_to<true>(&s.empty[st]);  // frees the stage in both CTAs
+          if (++kb == kb1) {
+            tc_commit_to<true>(&s.tmem_full[acc]);  // the segment's accumulator is complete: both CTAs' epilogues
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+          }
+        }
+        phase ^= 1u;
+      }
+      if (a.trace != nullptr) {
+        atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 5), static_cast<unsigned long long>(clock64() - t_start));
+        atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 6), 1ull);
+        atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 7), static_cast<unsigned long long>(total_it));
+        atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 0), static_cast<unsigned long long>(waited_acc));
+        atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 1), static_cast<unsigned long long>(waited_full));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------------ epilogue: 4 warps, 32 rows each
+    const int q = warp & 3;
+    uint8_t* obuf = s.out[warp - 2];
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    SegWalk walk(a, cluster, clusters);
+    int rb, ct, kb0, kb1;
+    while (ok && walk.next(rb, ct, kb0, kb1)) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&s.tmem_full[acc], acc_phase, abort_flag, a.sink, 34));
+      if (!ok) break;
+      tc_fence_after();
+      const int row0 = rb * 2 * kBM + static_cast<int>(rank) * kBM + q * 32;
+      const int col0 = ct * 256;
+      const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * 256);
+      const int chunks = (a.n - col0) > 128 ? 8 : 4;
+      const bool whole = kb0 == 0 && kb1 == a.k_blocks;
+      const float* other = nullptr;
+      bool write_out = whole;
+      if (!whole) {
+        // this tile is shared with the neighbouring cluster: side 1 continues what cluster - 1 began, side 0 begins
+        // what cluster + 1 continues. Store the partial, count in; the second of the two to arrive finishes the tile.
+        const int side = kb0 > 0 ? 1 : 0;
+        const size_t boundary = static_cast<size_t>(side ? cluster - 1 : cluster);
+        // a warp's share of a partial is private to the two warps (same rank, same quarter) that exchange it, so it
+        // is laid out for them: [chunk][float4 index][lane] - every store and load instruction moves 512 contiguous
+        // bytes (rows a kilobyte apart, one float4 per lane, took ten times as long)
+        float* mine = a.partials + ((((boundary * 2 + side) * 2 + rank) * 4 + q) * 8) * 1024 + lane * 4;
+        other = a.partials + ((((boundary * 2 + (side ^ 1)) * 2 + rank) * 4 + q) * 8) * 1024 + lane * 4;
+#pragma unroll 1
+        for (int ch = 0; ch < chunks; ++ch) {
+          float z[32];
+          tc_ld32(t_lane + ch * 32, z);
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            __stcg(reinterpret_cast<float4*>(mine + ch * 1024 + c * 128), make_float4(z[4 * c], z[4 * c + 1], z[4 * c + 2], z[4 * c + 3]));
+        }
+        __threadfence();
+        __syncwarp();
+        int old = 0;
+        if (lane == 0) old = atomicAdd(a.counters + (boundary * 2 + rank) * 4 + q, 1);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        write_out = old == 1;
+        if (write_out) __threadfence();
+      }
+      if (write_out) {
+        float4 o[4][8];  // the other cluster's partial, fetched four chunks (half a tile) at a time: the loads of a
+                         // lane are independent, and under a loaded memory system each round trip is microseconds
+#pragma unroll 1
+        for (int ch = 0; ch < chunks; ++ch) {
+          if (other != nullptr && (ch & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+              for (int c = 0; c < 8; ++c) o[j][c] = __ldcg(reinterpret_cast<const float4*>(other + (ch + j) * 1024 + c * 128));
+          }
+          float z[32];
+          tc_ld32(t_lane + ch * 32, z);
+          tc_wait_ld();
+          if (other != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (j == (ch & 3)) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                  z[4 * c] += o[j][c].x;
+                  z[4 * c + 1] += o[j][c].y;
+                  z[4 * c + 2] += o[j][c].z;
+                  z[4 * c + 3] += o[j][c].w;
+                }
+              }
+            }
+          }
+          if (lane == 0) bulk_wait_read_all();  // the previous block has left the staging memory
+          __syncwarp();
+          const int sw = (lane >> 1) & 3;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint4 pk;
+            pk.x = pack2<OUT>(z[c * 8 + 0], z[c * 8 + 1]);
+            pk.y = pack2<OUT>(z[c * 8 + 2], z[c * 8 + 3]);
+            pk.z = pack2<OUT>(z[c * 8 + 4], z[c * 8 + 5]);
+            pk.w = pack2<OUT>(z[c * 8 + 6], z[c * 8 + 7]);
+            *reinterpret_cast<uint4*>(obuf + lane * 64 + ((c ^ sw) << 4)) = pk;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          const int col = col0 + ch * 32;
+          if (lane == 0 && row0 < a.m && col < a.n) {
+            tma_store_2d(&map_c, obuf, col, row0);
+            bulk_commit();
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&s.tmem_empty[acc]), 0));  // the leader counts both CTAs
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (lane == 0) bulk_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees tensor memory or exits while the other may still signal it
+  tc_fence_after();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+static std::atomic<int> g_gemm_pair{-1};  // -1 = choose per problem, 0 = single-CTA tiles, 1 = CTA pairs
+
 // `inner` contiguous elements x `outer` rows of a 16-bit matrix as boxes of 64 x 64 with the 128-byte swizzle
 static bool make_map_mn(CUtensorMap* map, CUtensorMapDataType dt, const void* base, long long inner, long long outer) {
   EncodeTiledFn fn = encode_fn();
@@ -1181,6 +1551,8 @@ extern "C" void nd_tune_fc1_pair(int mode) { nd::g_fc1_pair.store(mode < 0 ? -1 
 // the copy-issuing thread waited for free stages, [3] cycles one epilogue warp waited for an accumulator, [4]
 // cycles that warp spent on tiles, [5] the copy-issuing thread's lifetime in cycles and [7] in nanoseconds (their
 // ratio is the SM clock during the launch). The two-CTA kernel reports [5] and [7] only. nullptr turns it off.
+extern "C" void nd_tune_fc1_bwd_pair(int mode) { nd::g_gemm_pair.store(mode < 0 ? -1 : (mode != 0 ? 1 : 0)); }
+
 extern "C" void nd_tune_fc1_trace(long long* device_counters) { nd::g_fc1_trace.store(device_counters); }
 
 extern "C" int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const void* x, const void* w,
@@ -1377,8 +1749,13 @@ extern "C" int nd_fc1_bwd_dz(int dtype, int act, const void* x, const void* w, c
 // The two GEMMs of the FC1 backward on the tcgen05 path, operands read where they lie (no transposes):
 //   op 0: c [m, n] = a [m, k] @ b [k, n]      (dx = dz @ W:   m tokens, k = 2I, n = H)
 //   op 1: c [m, n] = a [k, m]^T @ b [k, n]    (dW = dz^T @ x: m = 2I, k tokens, n = H)
+extern "C" size_t nd_fc1_bwd_gemm_ws_bytes(void) {
+  const int pairs = nd::sm_count() / 2;
+  return nd::kGpCounterBytes + static_cast<size_t>(pairs > 1 ? pairs - 1 : 0) * 4 * nd::kGpPartialFloats * sizeof(float);
+}
+
 extern "C" int nd_fc1_bwd_gemm(int dtype, int op, const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
-                               int* status, void* stream) {
+                               void* ws, size_t ws_bytes, int* status, void* stream) {
   using namespace nd;
   if (m < 0 || n <= 0 || k <= 0) return ND_ERR_BAD_ARG;
   if (dtype != ND_BF16 && dtype != ND_F16) return ND_ERR_UNSUPPORTED;
@@ -1410,6 +1787,74 @@ extern "C" int nd_fc1_bwd_gemm(int dtype, int op, const void* a, const void* b, 
         enc(&map_c, dt, 2, c, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return ND_ERR_LAUNCH;
+  }
+  const int pair_mode = g_gemm_pair.load();
+  const bool ws_ok = ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255u) == 0 && ws_bytes >= nd_fc1_bwd_gemm_ws_bytes();
+  // Whole 128 x 192 tiles waste the empty part of their last round over the SMs and the overhang of the last column
+  // tile; the evenly cut pair tiles waste only the overhang of the last 256-wide column tile (whose MMAs cost as much
+  // as a full tile's). Take the pairs where that is the smaller loss by a margin (measured: equal at 8192 x 1152,
+  // 8 - 15 % faster at 1024 / 1280 columns, 5 % slower where whole tiles already fill their rounds).
+  bool use_pairs = pair_mode == 1;
+  if (pair_mode < 0 && m > kBM) {
+    const long long rounds = (tiles + sm_count() - 1) / sm_count();
+    const double fill_single = static_cast<double>(tiles) / static_cast<double>(rounds * sm_count()) *
+                               static_cast<double>(n) / static_cast<double>(g.tiles_n * static_cast<long long>(kGemmBN));
+    const double fill_pair = static_cast<double>(n) / static_cast<double>(((n + 255) / 256) * 256);
+    use_pairs = fill_pair > 1.03 * fill_single;
+  }
+  if (ws_ok && sm_count() >= 4 && use_pairs) {
+    GemmPairArgs gp{};
+    gp.sink = g.sink;
+    gp.trace = g_fc1_trace.load(std::memory_order_relaxed);
+    gp.counters = static_cast<int*>(ws);
+    gp.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + kGpCounterBytes);
+    gp.m = g.m; gp.n = g.n; gp.k = g.k;
+    gp.tiles_n = static_cast<int>((n + 255) / 256);
+    gp.k_blocks = g.k_blocks;
+    const long long pair_tiles = ((m + 2 * kBM - 1) / (2 * kBM)) * gp.tiles_n;
+    gp.total_it = pair_tiles * gp.k_blocks;
+    const void* fnp;
+    if (dtype == ND_BF16)
+      fnp = op == 0 ? (const void*)gemm_bwd_pair_kernel<1, false, __nv_bfloat16>
+                    : (const void*)gemm_bwd_pair_kernel<1, true, __nv_bfloat16>;
+    else
+      fnp = op == 0 ? (const void*)gemm_bwd_pair_kernel<0, false, __half> : (const void*)gemm_bwd_pair_kernel<0, true, __half>;
+    const int smem_pair = static_cast<int>(sizeof(GemmPairSmem)) + 1024;
+    cudaError_t ep = cudaFuncSetAttribute(fnp, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_pair);
+    if (ep != cudaSuccess) {
+      set_last_cuda_error(ep);
+      (void)cudaGetLastError();
+      return ND_ERR_LAUNCH;
+    }
+    void* pp[] = {&map_a, &map_b, &map_c, &gp};
+    cudaLaunchConfig_t pc{};
+    pc.blockDim = dim3(kGemmThreads);
+    pc.dynamicSmemBytes = smem_pair;
+    pc.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    pc.attrs = &attr;
+    pc.numAttrs = 1;
+    pc.gridDim = dim3(static_cast<unsigned>(2 * (sm_count() / 2)));
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, fnp, &pc) != cudaSuccess || clusters < 1) {
+      (void)cudaGetLastError();
+      clusters = sm_count() / 2;
+    }
+    if (clusters > sm_count() / 2) clusters = sm_count() / 2;   // the workspace is sized for that many
+    if (clusters > pair_tiles) clusters = static_cast<int>(pair_tiles);  // a range is at least one tile long
+    pc.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+    ep = cudaMemsetAsync(ws, 0, kGpCounterBytes, pc.stream);
+    if (ep == cudaSuccess) ep = cudaLaunchKernelExC(&pc, fnp, pp);
+    if (ep != cudaSuccess) {
+      set_last_cuda_error(ep);
+      (void)cudaGetLastError();
+      return ND_ERR_LAUNCH;
+    }
+    return ND_OK;
   }
   const void* fn;
   if (dtype == ND_BF16)

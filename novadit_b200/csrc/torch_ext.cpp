@@ -378,8 +378,9 @@ at::Tensor fused_fc1_bias_act_backward_dx(const at::Tensor& dz, const at::Tensor
   c10::cuda::CUDAGuard guard(dz.device());
   at::Tensor dzc = dz.contiguous(), wc = weight.contiguous();
   at::Tensor dx = at::empty({dz.size(0), dz.size(1), weight.size(1)}, dz.options());
+  at::Tensor ws = at::empty({static_cast<int64_t>(nd_fc1_bwd_gemm_ws_bytes())}, dz.options().dtype(at::kByte));
   check_status(nd_fc1_bwd_gemm(dtype_id(dz), 0, dzc.data_ptr(), wc.data_ptr(), dx.data_ptr(), dz.size(0) * dz.size(1),
-                               weight.size(1), dz.size(2), nullptr, current_stream(dz)),
+                               weight.size(1), dz.size(2), ws.data_ptr(), ws.numel(), nullptr, current_stream(dz)),
                "fused_fc1_bias_act_backward_dx");
   return dx;
 }
@@ -395,8 +396,9 @@ at::Tensor fused_fc1_bias_act_backward_dw(const at::Tensor& dz, const at::Tensor
   c10::cuda::CUDAGuard guard(dz.device());
   at::Tensor dzc = dz.contiguous(), xc = x.contiguous();
   at::Tensor dw = at::empty({dz.size(2), x.size(2)}, dz.options());
+  at::Tensor ws = at::empty({static_cast<int64_t>(nd_fc1_bwd_gemm_ws_bytes())}, dz.options().dtype(at::kByte));
   check_status(nd_fc1_bwd_gemm(dtype_id(dz), 1, dzc.data_ptr(), xc.data_ptr(), dw.data_ptr(), dz.size(2), x.size(2),
-                               dz.size(0) * dz.size(1), nullptr, current_stream(dz)),
+                               dz.size(0) * dz.size(1), ws.data_ptr(), ws.numel(), nullptr, current_stream(dz)),
                "fused_fc1_bias_act_backward_dw");
   return dw;
 }

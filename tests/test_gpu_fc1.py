@@ -223,28 +223,50 @@ def test_unsupported_shapes_are_rejected_not_mangled():
                         y.data_ptr(), 8, 16, 8, None, st) == -2
 
 
+@pytest.fixture
+def pair_tiles():
+    """Forces whole single-CTA tiles (0) or evenly cut CTA-pair tiles (1) in nd_fc1_bwd_gemm for one test."""
+    lib = capi.lib()
+
+    def force(mode):
+        lib.nd_tune_fc1_bwd_pair(mode)
+
+    yield force
+    lib.nd_tune_fc1_bwd_pair(-1)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("m,n,k", [
     (256, 192, 128),      # exactly one row of tiles, two k-blocks
     (304, 264, 520),      # ragged in all three dimensions (row tile, column tile and k-block hang over)
     (1024, 1152, 2304),   # H = 1152: six column tiles, reduction over 2I = 2304
     (128, 64, 64),        # a single tile narrower than one box row
+    (6000, 1152, 520),    # 24 row blocks of five column tiles (the fifth a half tile): 120 tiles of 9 k-blocks cut
+                          # into 74 ranges of 14 / 15 k-blocks, most tiles shared by two CTA pairs
+    (520, 392, 72),       # a third, mostly empty row block; two column tiles, the second ragged
+    (8, 8, 8),            # smallest legal problem
 ])
-def test_backward_gemms_read_their_operands_in_place(dtype, m, n, k):
+@pytest.mark.parametrize("workspace", [False, True])
+def test_backward_gemms_read_their_operands_in_place(dtype, m, n, k, workspace, pair_tiles):
     """nd_fc1_bwd_gemm: op "dx" = a [m, k] @ b [k, n] (b MN-major), op "dw" = a [k, m]^T @ b [k, n] (both MN-major),
-    against the fp64 products of the same 16-bit inputs."""
+    against the fp64 products of the same 16-bit inputs; on whole 128 x 192 single-CTA tiles (no workspace) and on
+    the 256 x 256 tiles of CTA pairs with the reduction cut evenly over the pairs (workspace)."""
     gen = torch.Generator().manual_seed(m + n + k)
     a = (torch.randn(m, k, generator=gen) * 0.5).to(dtype)
     at = (torch.randn(k, m, generator=gen) * 0.5).to(dtype)
     b = (torch.randn(k, n, generator=gen) * 0.5).to(dtype)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    got = capi.fc1_bwd_gemm(a.to(DEV), b.to(DEV), "dx", status=status)
+    pair_tiles(1 if workspace else 0)  # with a workspace the library would otherwise choose per problem
+    got = capi.fc1_bwd_gemm(a.to(DEV), b.to(DEV), "dx", status=status, workspace=workspace)
     want = a.double() @ b.double()
     assert_half_parity_scaled(got.cpu(), want, f"dx gemm {dtype} {(m, n, k)}")
-    got = capi.fc1_bwd_gemm(at.to(DEV), b.to(DEV), "dw", status=status)
+    again = capi.fc1_bwd_gemm(a.to(DEV), b.to(DEV), "dx", status=status, workspace=workspace)
+    assert torch.equal(got, again), "the result must not depend on which CTA pair finishes a shared tile"
+    got = capi.fc1_bwd_gemm(at.to(DEV), b.to(DEV), "dw", status=status, workspace=workspace)
     want = at.double().T @ b.double()
     assert_half_parity_scaled(got.cpu(), want, f"dw gemm {dtype} {(m, n, k)}")
     assert int(status.item()) == 0
+    assert capi.lib().nd_device_error(0) == 0
 
 
 def assert_half_parity_scaled(got, want64, what):
