@@ -831,7 +831,8 @@ def run_gpu_arm(args) -> None:
 
 def run_profile_case(op: str, variant: int = -1) -> None:
     """A handful of direct launches (no graphs, no rotation) of one operator at its benchmark size: the
-    command ncu captures. `op`: norm (config 2 AdaLN fwd + bwd), rms, gate (2048 rows of config 3), fc1."""
+    command ncu captures. `op`: norm (config 2 AdaLN fwd + bwd), rms, gate (2048 rows of config 3), fc1, fc1_bwd,
+    residual."""
     from novadit_b200 import capi, synth
 
     dev = torch.device("cuda", 0)
@@ -856,6 +857,25 @@ def run_profile_case(op: str, variant: int = -1) -> None:
         for _ in range(3):
             capi.fc1_fwd(xf, wf, bf, "gelu", 1)
             capi.fc1_fwd(qx, qw, bf, "gelu", 1, alpha_dev=torch.cat([sx, sw]), out_dtype=torch.bfloat16)
+    elif op == "fc1_bwd":
+        # the FC1 backward at the DiT-XL/2 MLP shape: dz with recomputation, dx and dW (CTA-pair tiles), dbias
+        mt, hh, n2 = 8192, 1152, 9216
+        xb, wb, bb = (t.to(dev) for t in synth.fc1_inputs(mt, hh, n2, torch.bfloat16, seed=1))
+        dyb = torch.randn(mt, n2 // 2, device=dev).to(torch.bfloat16)
+        for _ in range(2):
+            dzb = capi.fc1_bwd_dz(xb, wb, bb, dyb, "gelu")
+            capi.fc1_bwd_gemm(dzb, wb, "dx")
+            capi.fc1_bwd_gemm(dzb, xb, "dw")
+            capi.colsum(dzb)
+    elif op == "residual":
+        # config 2 with the gated residual in front of the norm, and its backward partner
+        work = NormWorkload("layer", dev)
+        st = work.sets[0]
+        x, dy = st["x"], st["dy"]
+        gate = torch.randn(x.shape[0], x.shape[-1], device=dev).to(x.dtype)
+        for _ in range(3):
+            capi.norm_fwd_residual("layer", x, dy, gate, st["scale"], st["shift"], EPS)
+            capi.gated_residual_bwd_add(dy, x, dy, gate)
     else:
         raise SystemExit(f"unknown profile case {op}")
     torch.cuda.synchronize()

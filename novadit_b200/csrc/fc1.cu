@@ -1608,10 +1608,12 @@ extern "C" int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const
   const int g = gated;
   // Two-CTA tiles halve the B-operand bytes each SM stages and keep the tensor pipe busier per k-block, but the
   // pair's epilogues run in lockstep and a 256-row tile wastes more on small problems: measured faster for
-  // 16-bit operands once there are at least two rounds of single-CTA tiles, slower for FP8 (half the k-blocks
-  // per tile, so the epilogue weighs twice as much).
+  // 16-bit operands once there are at least two rounds of single-CTA tiles; for FP8 (half the k-blocks per
+  // tile, so the epilogue weighs twice as much) slower at K = 1152 (2168 against 2384 TFLOP/s at 8192 x 4608) and
+  // faster at K = 3072 (2635 against 2502 at 32768 x 12288): there the pairs start at 16 k-blocks.
   const int pair_mode = g_fc1_pair.load(std::memory_order_relaxed);
-  const bool pair = pair_mode >= 0 ? pair_mode != 0 : (ab_dtype != ND_E4M3 && tiles >= 2LL * sm_count());
+  const bool pair = pair_mode >= 0 ? pair_mode != 0
+                                   : (tiles >= 2LL * sm_count() && (ab_dtype != ND_E4M3 || a.k_blocks >= 16));
   const void* fn;
   if (pair) {
     if (ab_dtype == ND_E4M3)
