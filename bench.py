@@ -313,6 +313,29 @@ def bench_extras(dev, stream, hbm_peak: float, tf_peak: float, tf_sustained: flo
     out["adaln_fwd_bwd_pytorch_eager_cuda"] = {"GB/s": STEP_BYTES / ms / 1e6, "ms_per_step": ms}
     del work
 
+    # the gated residual in front of the norm: one launch (x_new = x + gate * branch, then AdaLN of x_new) against
+    # the two launches it replaces, over the same rotation of buffer sets (branch = the set's dy tensor)
+    work = NormWorkload("layer", dev)
+    gate = (torch.randn(B, H, device=dev) * 0.5).to(torch.bfloat16)
+
+    def fused_all():
+        for st in work.sets:
+            capi.norm_fwd_residual("layer", st["x"], st["dy"], gate, st["scale"], st["shift"], EPS)
+
+    def split_all():
+        for st in work.sets:
+            xn = capi.gated_residual_fwd(st["x"], st["dy"], gate)
+            capi.norm_fwd("layer", xn, st["scale"], st["shift"], EPS)
+
+    fused_all()
+    split_all()
+    ms_f = time_graph_loop(capture(fused_all), 20, stream) / NSETS
+    ms_s = time_graph_loop(capture(split_all), 20, stream) / NSETS
+    res_bytes = 4 * ROWS * H * 2  # x, branch in; x_new, y out
+    out["residual_adaln_fwd_fused"] = {"ms": ms_f, "GB/s": res_bytes / ms_f / 1e6,
+                                       "two_launches_ms": ms_s, "speedup_vs_two_launches": ms_s / ms_f}
+    del work
+
     # the same kernels on 16 x the rows (B = 512: 131 072 rows, 302 MB per tensor, two buffer sets): where launch
     # and first-byte latency stop mattering
     big_b = 16 * B
