@@ -98,3 +98,61 @@ def test_gate_act(ref, act, act_id):
     for name, r, m, w in (("y", ry, my, wy), ("dz", rdz, mdz, wdz)):
         close(r, w, f"reference kernel vs oracle {act} {name}")
         close(m, r, f"this library vs reference kernel {act} {name}")
+
+
+def _graph_ms(fn, reps=10):
+    """Milliseconds per call of fn(), replayed from a CUDA graph and timed with CUDA events."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            fn()
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            fn()
+    torch.cuda.synchronize()
+    for _ in range(3):
+        graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def test_speed_beside_the_reference_kernels(ref, record_property):
+    """The reference's kernels (built for sm_100) and this library's through the same pybind interface, outputs
+    allocated by the call, on the same buffers: gate-act forward + backward at workload config 3 (inputs far
+    larger than L2) and the AdaLN step at config 2 over 8 rotating buffer sets. The margins are wide on purpose (a
+    shared GPU): gate-act must not be slower than the reference's kernel by more than 3 %, AdaLN at least twice as
+    fast as its three launches."""
+    import novadit_b200.ops as ops
+
+    mine = ops.novadit_cuda
+    x, dy = synth.gate_act_inputs(32, 1024, 4608, torch.bfloat16, seed=3)
+    xd, gd = x.to(DEV), dy.to(DEV)
+    for act, act_id in (("silu", 0), ("gelu", 1)):
+        t_ref = _graph_ms(lambda: (ref.fused_gate_act_forward(xd, act_id), ref.fused_gate_act_backward(gd, xd, act_id)))
+        t_mine = _graph_ms(lambda: (mine.fused_gate_act_forward(xd, act_id), mine.fused_gate_act_backward(gd, xd, act_id)))
+        record_property(f"gate_act_{act}_fwd_bwd_ms_reference_vs_this", (t_ref, t_mine))
+        assert t_mine <= 1.03 * t_ref, f"gate-act {act}: this library {t_mine * 1e3:.1f} us, reference {t_ref * 1e3:.1f} us"
+    del xd, gd
+    b, s, h = 32, 256, 1152
+    x, scale, shift, dy = synth.norm_inputs(b, s, h, torch.bfloat16, seed=0)
+    sets = [(torch.roll(x, i, 1).to(DEV), scale.to(DEV), shift.to(DEV), torch.roll(dy, i, 1).to(DEV)) for i in range(8)]
+
+    def three_launches(mod):
+        def run():
+            for xs, sc, sh, g in sets:
+                _, _, mean, inv = mod.fused_adaln_forward(xs, sc, sh, 1e-6)
+                mod.fused_adaln_backward_dx(g, xs, sc, mean, inv)
+                mod.fused_adaln_backward_dparam(g, xs, mean, inv)
+        return run
+
+    t_ref = _graph_ms(three_launches(ref)) / 8
+    t_mine = _graph_ms(three_launches(mine)) / 8
+    record_property("adaln_fwd_dx_dparam_ms_reference_vs_this", (t_ref, t_mine))
+    assert t_mine <= 0.5 * t_ref, f"AdaLN step: this library {t_mine * 1e3:.1f} us, reference {t_ref * 1e3:.1f} us"
