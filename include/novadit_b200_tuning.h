@@ -41,6 +41,11 @@ void nd_tune_gate_act(int rows_per_group, int persistent);
 /* Tuning hook: 1 = two-CTA tiles (tcgen05 cta_group::2 over clusters of two CTAs), 0 = single-CTA
  * tiles, negative (default) = chosen per problem. Process-wide. No counterpart in the reference. */
 void nd_tune_fc1_pair(int mode);
+/* Tuning hook: 0 launches the FC1 kernels without programmatic stream serialization (default 1: barrier set-up,
+ * tensor-memory allocation and tensor-map prefetch of a launch may run while its predecessor in the stream drains;
+ * every kernel executes griddepcontrol.wait before its first global access). The CTA-pair backward GEMM, whose
+ * predecessor in the stream is a memset, is always launched without. */
+void nd_tune_fc1_pdl(int enabled);
 /* The same choice for the backward GEMMs (nd_fc1_bwd_gemm) when a workspace is given: 1 = 256 x 256 tiles over CTA
  * pairs with the k-blocks shared out evenly, 0 = whole 128 x 192 single-CTA tiles, negative (default) = chosen per
  * problem. Process-wide. No counterpart in the reference. */

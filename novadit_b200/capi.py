@@ -89,6 +89,7 @@ SIGNATURES = {
     "nd_tune_gate_act": (None, [c_int, c_int]),
     "nd_tune_fc1_pair": (None, [c_int]),
     "nd_tune_fc1_bwd_pair": (None, [c_int]),
+    "nd_tune_fc1_pdl": (None, [c_int]),
     "nd_tune_fc1_trace": (None, [c_void_p]),
     "nd_amax_ws_bytes": (c_size_t, []),
     "nd_amax": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),

@@ -513,6 +513,11 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s.tmem_base;
+  // Programmatic dependent launch: everything above (barriers, tensor memory, tensor-map prefetch) touches no global
+  // memory and may run while the previous kernel in the stream drains; nothing below runs before that kernel has
+  // completed and its writes are visible. A launch without the attribute passes both instructions at once.
+  griddep_launch_dependents();
+  griddep_wait();
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer (one thread)
@@ -733,6 +738,11 @@ fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   cluster_sync_all();  // the peer's barriers exist before anything is signalled across the pair
   tc_fence_after();
   const uint32_t tmem_base = s.tmem_base;
+  // Programmatic dependent launch: everything above (barriers, tensor memory, tensor-map prefetch) touches no global
+  // memory and may run while the previous kernel in the stream drains; nothing below runs before that kernel has
+  // completed and its writes are visible. A launch without the attribute passes both instructions at once.
+  griddep_launch_dependents();
+  griddep_wait();
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer (one thread in each CTA)
@@ -890,6 +900,7 @@ static const void* pick_fc1_pair(int act, int gated) {
   }
 }
 
+static std::atomic<int> g_fc1_pdl{1};    // 1 = launch with programmatic stream serialization
 static std::atomic<int> g_fc1_pair{-1};  // -1 = choose per problem
 static std::atomic<long long*> g_fc1_trace{nullptr};
 
@@ -989,6 +1000,11 @@ gemm_bwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s.tmem_base;
+  // Programmatic dependent launch: everything above (barriers, tensor memory, tensor-map prefetch) touches no global
+  // memory and may run while the previous kernel in the stream drains; nothing below runs before that kernel has
+  // completed and its writes are visible. A launch without the attribute passes both instructions at once.
+  griddep_launch_dependents();
+  griddep_wait();
 
   if (warp == 0) {
     if (lane == 0) {  // ---------------------------------------------------------- copies
@@ -1274,6 +1290,11 @@ gemm_bwd_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   cluster_sync_all();  // the peer's barriers exist before anything is signalled across the pair
   tc_fence_after();
   const uint32_t tmem_base = s.tmem_base;
+  // Programmatic dependent launch: everything above (barriers, tensor memory, tensor-map prefetch) touches no global
+  // memory and may run while the previous kernel in the stream drains; nothing below runs before that kernel has
+  // completed and its writes are visible. A launch without the attribute passes both instructions at once.
+  griddep_launch_dependents();
+  griddep_wait();
 
   if (warp == 0) {
     if (lane == 0) {  // ---------------------------------------------------------- copies (one thread in each CTA)
@@ -1551,6 +1572,8 @@ extern "C" void nd_tune_fc1_pair(int mode) { nd::g_fc1_pair.store(mode < 0 ? -1 
 // the copy-issuing thread waited for free stages, [3] cycles one epilogue warp waited for an accumulator, [4]
 // cycles that warp spent on tiles, [5] the copy-issuing thread's lifetime in cycles and [7] in nanoseconds (their
 // ratio is the SM clock during the launch). The two-CTA kernel reports [5] and [7] only. nullptr turns it off.
+extern "C" void nd_tune_fc1_pdl(int enabled) { nd::g_fc1_pdl.store(enabled != 0 ? 1 : 0); }
+
 extern "C" void nd_tune_fc1_bwd_pair(int mode) { nd::g_gemm_pair.store(mode < 0 ? -1 : (mode != 0 ? 1 : 0)); }
 
 extern "C" void nd_tune_fc1_trace(long long* device_counters) { nd::g_fc1_trace.store(device_counters); }
@@ -1645,15 +1668,21 @@ extern "C" int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = static_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attr{};
+  // attribute 0: programmatic stream serialization (the kernel's prologue may run while its predecessor in the
+  // stream drains; see griddep_wait in the kernels); attribute 1, pairs only: the cluster shape
+  cudaLaunchAttribute attrs[2] = {};
+  attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[0].val.programmaticStreamSerializationAllowed = g_fc1_pdl.load(std::memory_order_relaxed) != 0 ? 1 : 0;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 1;
   if (pair) {
     // persistent grid of CTA pairs: as many clusters of two as can be resident, at most one per tile
+    cudaLaunchAttribute& attr = attrs[1];
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = 2;
     attr.val.clusterDim.y = 1;
     attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     const long long pair_tiles = static_cast<long long>((a.m + 2 * kBM - 1) / (2 * kBM)) * a.tiles_n;
     cfg.gridDim = dim3(static_cast<unsigned>(2 * (sm_count() / 2)));
     int clusters = 0;
@@ -1738,8 +1767,19 @@ extern "C" int nd_fc1_bwd_dz(int dtype, int act, const void* x, const void* w, c
   }
   void* params[] = {&map_x, &map_w, &map_dzg, &map_dzv, &map_dy, &a};
   const long long grid = tiles < sm_count() ? tiles : sm_count();
-  e = cudaLaunchKernel(fn, dim3(static_cast<unsigned>(grid)), dim3(kThreads), params, smem_bytes,
-                       static_cast<cudaStream_t>(stream));
+  {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = g_fc1_pdl.load(std::memory_order_relaxed) != 0 ? 1 : 0;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelExC(&cfg, fn, params);
+  }
   if (e != cudaSuccess) {
     set_last_cuda_error(e);
     (void)cudaGetLastError();
@@ -1876,6 +1916,11 @@ extern "C" int nd_fc1_bwd_gemm(int dtype, int op, const void* a, const void* b, 
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = static_cast<cudaStream_t>(stream);
   cfg.gridDim = dim3(static_cast<unsigned>(tiles < sm_count() ? tiles : sm_count()));
+  cudaLaunchAttribute pdl{};
+  pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl.val.programmaticStreamSerializationAllowed = g_fc1_pdl.load(std::memory_order_relaxed) != 0 ? 1 : 0;
+  cfg.attrs = &pdl;
+  cfg.numAttrs = 1;
   e = cudaLaunchKernelExC(&cfg, fn, params);
   if (e != cudaSuccess) {
     set_last_cuda_error(e);
