@@ -445,6 +445,9 @@ def bench_extras(dev, stream, hbm_peak: float, tf_peak: float, tf_sustained: flo
     gf = 2.0 * mt * hh * n2
     ms = time_graph_loop(capture(lambda: capi.fc1_bwd_dz(xb_, wb_, bb_, dyb, "gelu", status=status)), 20, stream)
     out["fc1_bwd_dz_recompute"] = {"TFLOP/s": gf / ms / 1e9, "ms": ms}
+    capi.fc1_bwd_dz_dbias(xb_, wb_, bb_, dyb, "gelu", status=status)
+    ms = time_graph_loop(capture(lambda: capi.fc1_bwd_dz_dbias(xb_, wb_, bb_, dyb, "gelu", status=status)), 20, stream)
+    out["fc1_bwd_dz_recompute_with_dbias"] = {"TFLOP/s": gf / ms / 1e9, "ms": ms}
     for name, fn, lib in (("dx", lambda: capi.fc1_bwd_gemm(dzb, wb_, "dx", status=status), lambda: dzb @ wb_),
                           ("dw", lambda: capi.fc1_bwd_gemm(dzb, xb_, "dw", status=status), lambda: dzb.t() @ xb_)):
         fn()

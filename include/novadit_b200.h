@@ -268,6 +268,16 @@ int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const void* x, c
 int nd_fc1_bwd_dz(int dtype, int act, const void* x, const void* w, const void* bias, const void* dy,
                   void* dz, int64_t m, int64_t k, int64_t n, int* status, void* stream);
 
+/* nd_fc1_bwd_dz that also returns dbias [n] = the sum of dz over the m tokens (of the values as stored, i.e. rounded
+ * to the element type, accumulated in fp32 in a fixed order: the `dz_flat.sum(dim=0)` of
+ * novadit/ops/fc1_bias_act.py:279) without reading dz again: each epilogue warp leaves the column sums of its 32
+ * rows in `ws` (nd_fc1_bwd_dbias_ws_bytes(m, n) bytes, 16-byte aligned, no initialisation needed), a second small
+ * launch adds them in row order. dbias has the element type of dz. */
+size_t nd_fc1_bwd_dbias_ws_bytes(int64_t m, int64_t n);
+int nd_fc1_bwd_dz_dbias(int dtype, int act, const void* x, const void* w, const void* bias, const void* dy,
+                        void* dz, void* dbias, void* ws, size_t ws_bytes, int64_t m, int64_t k, int64_t n,
+                        int* status, void* stream);
+
 /* The two GEMMs of the FC1 backward on the tcgen05 path, fp32 accumulation, operands read where they lie (UMMA
  * takes W and, for dW, dz as MN-major operands: no transpose copy per call, unlike the reference's
  * _backward_dx_cute, novadit/ops/fc1_bias_act.py:309-315, which copies and transposes both weight halves):

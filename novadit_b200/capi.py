@@ -81,6 +81,9 @@ SIGNATURES = {
                            c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "nd_fc1_bwd_dz": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                               c_int64, c_void_p, c_void_p]),
+    "nd_fc1_bwd_dbias_ws_bytes": (c_size_t, [c_int64, c_int64]),
+    "nd_fc1_bwd_dz_dbias": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_size_t, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "nd_fc1_bwd_gemm_ws_bytes": (c_size_t, []),
     "nd_fc1_bwd_gemm": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_size_t,
                                 c_void_p, c_void_p]),
@@ -411,6 +414,22 @@ def fc1_bwd_dz(x, w, bias, dy, act="silu", status=None):
     check(lib().nd_fc1_bwd_dz(DTYPE_IDS[x.dtype], ACT_IDS[act], _ptr(x), _ptr(w), _ptr(bias), _ptr(dy), _ptr(dz),
                               m, k, n, _ptr(status), _stream()), "nd_fc1_bwd_dz")
     return dz
+
+
+def fc1_bwd_dz_dbias(x, w, bias, dy, act="silu", status=None):
+    """(dz, dbias) of the gated FC1: dz as fc1_bwd_dz, dbias [N] = dz summed over the tokens inside the same launch."""
+    _need_cuda(x, w, bias, dy)
+    k = x.shape[-1]
+    m = x.numel() // k
+    n = w.shape[0]
+    L = lib()
+    dz = torch.empty(*x.shape[:-1], n, dtype=x.dtype, device=x.device)
+    dbias = torch.empty(n, dtype=x.dtype, device=x.device)
+    ws = torch.empty(max(L.nd_fc1_bwd_dbias_ws_bytes(m, n), 16), dtype=torch.uint8, device=x.device)
+    check(L.nd_fc1_bwd_dz_dbias(DTYPE_IDS[x.dtype], ACT_IDS[act], _ptr(x), _ptr(w), _ptr(bias), _ptr(dy), _ptr(dz),
+                                _ptr(dbias), _ptr(ws), ws.numel(), m, k, n, _ptr(status), _stream()),
+          "nd_fc1_bwd_dz_dbias")
+    return dz, dbias
 
 
 _GEMM_WS: dict = {}

@@ -60,6 +60,7 @@ struct Fc1Args {
   const float* alpha_dev;  // nullable, two floats multiplied into alpha
   Fc1Sink sink;
   long long* trace;        // nullable: per-role cycle counters (see nd_tune_fc1_trace)
+  float* dbias_part;       // nullable (backward only): [tiles_m * 4][n] column sums of dz per 32-row quarter
   float alpha_host;
   int m, k, n;             // n = rows of w
   int n_out;               // columns of y (n/2 gated, n plain)
@@ -299,6 +300,22 @@ __device__ __forceinline__ void epilogue_columns(const Fc1Args& a, const CUtenso
   }
 }
 
+// Column sums over the 32 lanes of a warp of 32 values each (lane = row, index = column): five exchange rounds,
+// each halving the values a lane holds; lane l ends with the sum of column l, added up in a fixed order.
+__device__ __forceinline__ float warp_colsum32(float (&v)[32], int lane) {
+#pragma unroll
+  for (int half = 16; half >= 1; half >>= 1) {
+    const bool upper = (lane & half) != 0;
+#pragma unroll
+    for (int i = 0; i < half; ++i) {
+      const float send = upper ? v[i] : v[i + half];
+      const float keep = upper ? v[i + half] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+    }
+  }
+  return v[0];
+}
+
 // Backward of the gated activation in the epilogue (stacked gating only): the accumulators are the recomputed
 // pre-activations z = x W^T + b of the tile, and with the 32 x 32 block of dy fetched by the copy engine into
 // the warp's first staging block,
@@ -380,6 +397,24 @@ __device__ __forceinline__ void epilogue_columns_bwd(const Fc1Args& a, const CUt
       tma_store_2d(map_dzg, blk_g, col, row0);
       tma_store_2d(map_dzv, blk_v, col, row0);
       bulk_commit();
+    }
+    if (a.dbias_part != nullptr) {
+      // dbias = sum of dz over the tokens, of the values as they are STORED (rounded to the element type, like the
+      // reference's dz.sum(0)): this warp's 32 rows give one partial per column, the second stage adds the
+      // partials of all row quarters in order. Rows past m and columns past n_out hold zeros (dy is zero there).
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const float2 rg = unpack_pair<OUT>(pack2<OUT>(dg[j], dg[j + 1]));
+        const float2 rv = unpack_pair<OUT>(pack2<OUT>(dv[j], dv[j + 1]));
+        dg[j] = rg.x; dg[j + 1] = rg.y;
+        dv[j] = rv.x; dv[j + 1] = rv.y;
+      }
+      const float sg = warp_colsum32(dg, lane), sv = warp_colsum32(dv, lane);
+      if (col + lane < a.n_out) {
+        float* row = a.dbias_part + static_cast<size_t>(row0 >> 5) * a.n;
+        row[col + lane] = sg;
+        row[a.n_out + col + lane] = sv;
+      }
     }
   }
 }
@@ -1572,6 +1607,24 @@ extern "C" void nd_tune_fc1_pair(int mode) { nd::g_fc1_pair.store(mode < 0 ? -1 
 // the copy-issuing thread waited for free stages, [3] cycles one epilogue warp waited for an accumulator, [4]
 // cycles that warp spent on tiles, [5] the copy-issuing thread's lifetime in cycles and [7] in nanoseconds (their
 // ratio is the SM clock during the launch). The two-CTA kernel reports [5] and [7] only. nullptr turns it off.
+// dbias [cols] = sum over `rows` partial rows of part [rows, cols] (fp32), in row order
+template <typename T>
+__global__ void __launch_bounds__(256) dbias_stage2(const float* __restrict__ part, T* __restrict__ out, int rows, int cols) {
+  nd::griddep_wait();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= cols) return;
+  float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;  // four interleaved chains, combined in a fixed order
+  int r = 0;
+  for (; r + 4 <= rows; r += 4) {
+    acc0 += part[static_cast<size_t>(r) * cols + c];
+    acc1 += part[static_cast<size_t>(r + 1) * cols + c];
+    acc2 += part[static_cast<size_t>(r + 2) * cols + c];
+    acc3 += part[static_cast<size_t>(r + 3) * cols + c];
+  }
+  for (; r < rows; ++r) acc0 += part[static_cast<size_t>(r) * cols + c];
+  out[c] = nd::from_f32<T>((acc0 + acc1) + (acc2 + acc3));
+}
+
 extern "C" void nd_tune_fc1_pdl(int enabled) { nd::g_fc1_pdl.store(enabled != 0 ? 1 : 0); }
 
 extern "C" void nd_tune_fc1_bwd_pair(int mode) { nd::g_gemm_pair.store(mode < 0 ? -1 : (mode != 0 ? 1 : 0)); }
@@ -1709,20 +1762,55 @@ extern "C" int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const
 // eager PyTorch (novadit/ops/fc1_bias_act.py:255-270). Here both happen in ONE launch of the forward kernel's main
 // loop with the activation backward as its epilogue: dz [m, n] = [dy * value * act'(gate) | dy * act(gate)] for
 // w rows [gate | value]; z never reaches memory. 16-bit operands, single-CTA tiles.
+extern "C" size_t nd_fc1_bwd_dbias_ws_bytes(int64_t m, int64_t n) {
+  if (m <= 0 || n <= 0) return 0;
+  return static_cast<size_t>((m + nd::kBM - 1) / nd::kBM) * 4 * static_cast<size_t>(n) * sizeof(float);
+}
+
+static int fc1_bwd_dz_impl(int dtype, int act, const void* x, const void* w, const void* bias, const void* dy, void* dz,
+                           void* dbias, void* ws, size_t ws_bytes, int64_t m, int64_t k, int64_t n, int* status,
+                           void* stream);
+
 extern "C" int nd_fc1_bwd_dz(int dtype, int act, const void* x, const void* w, const void* bias, const void* dy,
                              void* dz, int64_t m, int64_t k, int64_t n, int* status, void* stream) {
+  return fc1_bwd_dz_impl(dtype, act, x, w, bias, dy, dz, nullptr, nullptr, 0, m, k, n, status, stream);
+}
+
+extern "C" int nd_fc1_bwd_dz_dbias(int dtype, int act, const void* x, const void* w, const void* bias, const void* dy,
+                                   void* dz, void* dbias, void* ws, size_t ws_bytes, int64_t m, int64_t k, int64_t n,
+                                   int* status, void* stream) {
+  if (!dbias || !ws) return ND_ERR_BAD_ARG;
+  return fc1_bwd_dz_impl(dtype, act, x, w, bias, dy, dz, dbias, ws, ws_bytes, m, k, n, status, stream);
+}
+
+static int fc1_bwd_dz_impl(int dtype, int act, const void* x, const void* w, const void* bias, const void* dy, void* dz,
+                           void* dbias, void* ws, size_t ws_bytes, int64_t m, int64_t k, int64_t n, int* status,
+                           void* stream) {
   using namespace nd;
   if (m < 0 || k <= 0 || n <= 0 || (n % 2) != 0) return ND_ERR_BAD_ARG;
   if (act != ND_ACT_SILU && act != ND_ACT_GELU) return ND_ERR_UNSUPPORTED;
   if (dtype != ND_BF16 && dtype != ND_F16) return ND_ERR_UNSUPPORTED;
-  if (m == 0) return ND_OK;
+  if (m == 0) {
+    if (dbias != nullptr) {  // no tokens: the sum over them is zero
+      cudaError_t ez = cudaMemsetAsync(dbias, 0, static_cast<size_t>(n) * 2, static_cast<cudaStream_t>(stream));
+      if (ez != cudaSuccess) {
+        set_last_cuda_error(ez);
+        (void)cudaGetLastError();
+        return ND_ERR_LAUNCH;
+      }
+    }
+    return ND_OK;
+  }
   if (!x || !w || !dy || !dz) return ND_ERR_BAD_ARG;
   const long long n_out = n / 2;
   if ((k * 2) % 16 != 0 || n_out % 8 != 0) return ND_ERR_UNSUPPORTED;
   if (!aligned16(x) || !aligned16(w) || !aligned16(dy) || !aligned16(dz)) return ND_ERR_UNSUPPORTED;
   if (m > INT32_MAX - kBM || n > INT32_MAX - kBN || k > INT32_MAX - 256) return ND_ERR_UNSUPPORTED;
+  if (dbias != nullptr && ((reinterpret_cast<uintptr_t>(ws) & 15u) != 0 || ws_bytes < nd_fc1_bwd_dbias_ws_bytes(m, n)))
+    return ND_ERR_BAD_ARG;
 
   Fc1Args a{};
+  a.dbias_part = dbias != nullptr ? static_cast<float*>(ws) : nullptr;
   a.bias = bias; a.y = dz; a.sink = Fc1Sink{status, device_error_ptr()}; a.alpha_host = 1.f;
   a.m = static_cast<int>(m); a.k = static_cast<int>(k); a.n = static_cast<int>(n);
   a.n_out = static_cast<int>(n_out);
@@ -1784,6 +1872,20 @@ extern "C" int nd_fc1_bwd_dz(int dtype, int act, const void* x, const void* w, c
     set_last_cuda_error(e);
     (void)cudaGetLastError();
     return ND_ERR_LAUNCH;
+  }
+  if (dbias != nullptr) {
+    const int rows = a.tiles_m * 4, cols = a.n;
+    const unsigned blocks = static_cast<unsigned>((cols + 255) / 256);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == ND_BF16)
+      dbias_stage2<__nv_bfloat16><<<blocks, 256, 0, st>>>(a.dbias_part, static_cast<__nv_bfloat16*>(dbias), rows, cols);
+    else
+      dbias_stage2<__half><<<blocks, 256, 0, st>>>(a.dbias_part, static_cast<__half*>(dbias), rows, cols);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      set_last_cuda_error(e);
+      return ND_ERR_LAUNCH;
+    }
   }
   return ND_OK;
 }

@@ -364,6 +364,40 @@ at::Tensor fused_fc1_bias_act_backward_dz(const at::Tensor& x, const at::Tensor&
   return dz;
 }
 
+// The same launch returning dbias [2I] as well (dz summed over the tokens inside the epilogue, a second small launch
+// adds the per-warp partials): the `dz_flat.sum(dim=0)` of novadit/ops/fc1_bias_act.py:279 without reading dz again.
+std::vector<at::Tensor> fused_fc1_bias_act_backward_dz_dbias(const at::Tensor& x, const at::Tensor& weight,
+                                                             c10::optional<at::Tensor> bias, const at::Tensor& dy,
+                                                             int64_t act_id) {
+  TORCH_CHECK(x.is_cuda() && weight.is_cuda() && dy.is_cuda(), "x, weight and dy must be CUDA tensors");
+  TORCH_CHECK(x.dim() == 3 && weight.dim() == 2 && weight.size(1) == x.size(2) && weight.size(0) % 2 == 0,
+              "x must be [batch, seq, hidden] and weight [2 * intermediate, hidden]");
+  TORCH_CHECK(dy.dim() == 3 && dy.size(0) == x.size(0) && dy.size(1) == x.size(1) && dy.size(2) * 2 == weight.size(0),
+              "dy must have shape [batch, seq, intermediate]");
+  TORCH_CHECK(x.scalar_type() == weight.scalar_type() && x.scalar_type() == dy.scalar_type(), "x, weight, dy: one dtype");
+  TORCH_CHECK(x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16, "fp16 and bf16 only");
+  TORCH_CHECK(act_id == 0 || act_id == 1, "act_id must be 0 (SiLU) or 1 (GELU)");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor xc = x.contiguous(), wc = weight.contiguous(), dyc = dy.contiguous(), bc;
+  const void* bias_p = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_cuda() && bias->numel() == weight.size(0) && bias->scalar_type() == x.scalar_type(),
+                "bias must be a CUDA tensor of 2 * intermediate elements with x's dtype");
+    bc = bias->contiguous();
+    bias_p = bc.data_ptr();
+  }
+  const int64_t m = x.size(0) * x.size(1), n = weight.size(0);
+  at::Tensor dz = at::empty({x.size(0), x.size(1), n}, x.options());
+  at::Tensor dbias = at::empty({n}, x.options());
+  const int64_t ws_bytes = static_cast<int64_t>(nd_fc1_bwd_dbias_ws_bytes(m, n));
+  at::Tensor ws = at::empty({ws_bytes > 16 ? ws_bytes : 16}, x.options().dtype(at::kByte));
+  check_status(nd_fc1_bwd_dz_dbias(dtype_id(x), static_cast<int>(act_id), xc.data_ptr(), wc.data_ptr(), bias_p,
+                                   dyc.data_ptr(), dz.data_ptr(), dbias.data_ptr(), ws.data_ptr(), ws.numel(), m,
+                                   x.size(2), n, nullptr, current_stream(x)),
+               "fused_fc1_bias_act_backward_dz_dbias");
+  return {dz, dbias};
+}
+
 // dx = dz @ weight for dz [B, S, 2I] and the FC1 weight [2I, H]: the job of the reference's CuTe-DSL backward-dx
 // kernel (csrc/cute_dsl/fc1_bias_act/fc1_bias_act.py:996-1913 behind novadit/ops/fc1_bias_act.py:288-326), on the
 // tcgen05 GEMM that reads the weight in place as an MN-major operand (the reference copies and transposes both
@@ -714,6 +748,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         "fused FC1 + bias + gated activation; weight rows [gate block | value block]");
   m.def("fused_fc1_bias_act_backward_dz", &fused_fc1_bias_act_backward_dz,
         "dz of the gated FC1 with z recomputed inside the kernel");
+  m.def("fused_fc1_bias_act_backward_dz_dbias", &fused_fc1_bias_act_backward_dz_dbias,
+        "[dz, dbias] of the gated FC1: z recomputed and dz summed over the tokens inside one kernel");
   m.def("fused_fc1_bias_act_backward_dx", &fused_fc1_bias_act_backward_dx, "dx = dz @ weight on the tcgen05 GEMM");
   m.def("fused_fc1_bias_act_forward_plain", &fused_fc1_bias_act_forward_plain,
         "fused FC1 + bias + activation without gating, y = act(x W^T + b)");

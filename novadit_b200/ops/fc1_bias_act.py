@@ -69,25 +69,34 @@ class _FusedFc1BiasActFunction(torch.autograd.Function):
         x, weight, bias = ctx.saved_tensors
         ext = require_cuda_extension("fused_fc1_bias_act", x, "fc1_bias_act_ref")
         inter, hidden = weight.shape[0] // 2, weight.shape[1]
+        want_db = bias is not None and ctx.needs_input_grad[2]
+        d_b = None
         if hidden % 8 == 0 and inter % 8 == 0:
-            # z recomputed and differentiated inside one tcgen05 launch: it never reaches memory
-            dz = ext.fused_fc1_bias_act_backward_dz(x, weight, bias, dy, ctx.act_id)
+            # z recomputed and differentiated inside one tcgen05 launch: it never reaches memory; dbias is summed
+            # in the same epilogue, so dz is not read a second time for it
+            if want_db:
+                dz, d_b = ext.fused_fc1_bias_act_backward_dz_dbias(x, weight, bias, dy, ctx.act_id)
+            else:
+                dz = ext.fused_fc1_bias_act_backward_dz(x, weight, bias, dy, ctx.act_id)
         else:
             z = F.linear(x, weight, bias)  # recomputed, as in the reference
             dz = ext.fused_gate_act_backward_gate_first(dy.contiguous(), z, ctx.act_id)  # one pass, not ~8 eager ones
         if hidden % 8 == 0 and inter % 4 == 0:
-            # dx = dz W and dW = dz^T x on the tcgen05 GEMM that reads W, dz and x in place (MN-major operands, 128 x
-            # 192 tiles), dbias by the two-stage column sum: no library GEMM or reduction in the backward pass
+            # dx = dz W and dW = dz^T x on the tcgen05 GEMMs that read W, dz and x in place (MN-major operands);
+            # dbias by the two-stage column sum where the dz launch has not produced it: no library GEMM or
+            # reduction in the backward pass
             dx = ext.fused_fc1_bias_act_backward_dx(dz, weight) if ctx.needs_input_grad[0] else None
             d_w = ext.fused_fc1_bias_act_backward_dw(dz, x) if ctx.needs_input_grad[1] else None
-            d_b = ext.fused_fc1_bias_act_backward_dbias(dz) if bias is not None and ctx.needs_input_grad[2] else None
+            if want_db and d_b is None:
+                d_b = ext.fused_fc1_bias_act_backward_dbias(dz)
             return dx, d_w, d_b, None
         # rows the copy engine cannot walk (pitches that are not multiples of 16 bytes): PyTorch's GEMMs
         m = x.shape[0] * x.shape[1]
         dz_flat, x_flat = dz.reshape(m, -1), x.reshape(m, -1)
         dx = (dz_flat @ weight).reshape(x.shape)
         d_w = dz_flat.T @ x_flat
-        d_b = dz_flat.sum(dim=0) if bias is not None else None
+        if want_db and d_b is None:
+            d_b = dz_flat.sum(dim=0)
         return dx, d_w, d_b, None
 
 

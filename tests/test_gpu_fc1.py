@@ -98,6 +98,34 @@ def test_backward_dz_kernel_matches_oracle(act, dtype, mkn, bias):
     assert_half_parity(dz.cpu(), want.to(dtype), f"dz {act} {dtype} {mkn}", exact=want)
 
 
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+@pytest.mark.parametrize("dtype,mkn", [
+    (torch.bfloat16, (300, 200, 272)),     # ragged row tile, ragged column chunk (136 outputs: 4 full chunks + 8)
+    (torch.float16, (129, 1152, 528)),
+    (torch.bfloat16, (1, 64, 16)),
+    (torch.bfloat16, (2048, 1152, 9216)),  # DiT-XL/2 MLP width: 16 row tiles x 4 quarters of partial sums
+])
+def test_backward_dz_with_dbias_in_the_epilogue(act, dtype, mkn):
+    """nd_fc1_bwd_dz_dbias: the same dz bit for bit, and dbias = the fp32 sum over the tokens of the STORED dz."""
+    m, k, n = mkn
+    x, w, b = synth.fc1_inputs(m, k, n, dtype, seed=73)
+    dy = torch.randn(m, n // 2, generator=torch.Generator().manual_seed(74)).to(dtype)
+    status = new_status()
+    args = (x.to(DEV), w.to(DEV), b.to(DEV), dy.to(DEV), act)
+    dz_only = capi.fc1_bwd_dz(*args, status=status)
+    dz, dbias = capi.fc1_bwd_dz_dbias(*args, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(dz, dz_only)
+    want = dz.double().sum(dim=0)
+    # fp32 accumulation of up to m terms, then one rounding to the element type
+    scale = dz.double().abs().sum(dim=0).clamp_min(1e-30)
+    err = (dbias.double() - want).abs()
+    assert bool((err <= 1e-6 * scale + torch.finfo(dtype).eps * want.abs() + 1e-30).all()), float((err / scale).max())
+    again = capi.fc1_bwd_dz_dbias(*args, status=status)[1]
+    assert torch.equal(dbias, again)
+
+
 def test_backward_dx_binding_matches_matmul():
     gen = torch.Generator().manual_seed(8)
     dz = torch.randn(2, 150, 512, generator=gen).to(DEV, torch.bfloat16)
