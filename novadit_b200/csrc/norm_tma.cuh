@@ -460,6 +460,219 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma(const NormArgs a) {
   }
 }
 
+// The forward with the flat walk of norm_bwd_tma_flat (below): every chunk lies inside one sample, so the modulation
+// vectors are loaded once, positions are 32-bit offsets from bases computed once, and full groups run without row
+// predicates. Same arithmetic in the same order as norm_fwd_tma: bit-identical results.
+template <typename T, int VEC, int RPI, int MAXR, bool RMS, bool RES = false>
+__global__ void __maxnreg__(MAXR) norm_fwd_tma_flat(const NormArgs a) {
+  constexpr int NP = VEC / 2;
+  extern __shared__ __align__(128) unsigned char dsm[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(dsm);
+  unsigned char* buf = dsm + kBarrierBytes;
+  __shared__ __align__(16) float red[2][RPI * 32];
+  __shared__ __align__(16) float zero16[4];  // what idle lanes of the last warp read instead of a column
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
+  if (tid < 4) zero16[tid] = 0.f;
+  if (tid == 0) s_abort = 0;
+
+  const int H = a.hidden;
+  const uint32_t row_bytes = static_cast<uint32_t>(H) * sizeof(T);
+  const uint32_t stage_total = (RES ? 2 : 1) * RPI * row_bytes;  // x rows [then branch rows]
+  const bool active = tid < H / VEC;
+  const int col = active ? tid * VEC : 0;
+  const uint32_t src_stride = active ? row_bytes : 0u;
+  [[maybe_unused]] const uint32_t br_off = active ? RPI * row_bytes : 0u;
+  const float inv_h = 1.f / static_cast<float>(H);
+  const float eps = a.eps;
+
+  // this CTA's chunk: rows [r0, r0 + n) of sample bi of the shard (whole samples, cut evenly)
+  const int k = a.chunks_per_sample, seq = static_cast<int>(a.seq_len);
+  const int bi = static_cast<int>(blockIdx.x) / k, cj = static_cast<int>(blockIdx.x) - bi * k;
+  const int cbase = seq / k, crem = seq - cbase * k;
+  const long long r0 = static_cast<long long>(bi) * seq + cj * cbase + (cj < crem ? cj : crem);
+  const int n = cbase + (cj < crem ? 1 : 0);
+  const int n_groups = (n + RPI - 1) / RPI;
+  const long long b = a.b_first + bi;
+
+  if (tid == 0) {
+    for (int s = 0; s < a.stages; ++s) mbar_init(&full[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  griddep_launch_dependents();
+  __syncthreads();
+  griddep_wait();  // nothing above reads global memory; everything below may
+
+  const T* xg = static_cast<const T*>(a.x) + r0 * H;
+  [[maybe_unused]] const T* bg = RES ? static_cast<const T*>(a.dy) + r0 * H : nullptr;
+  int pg = 0;  // next group to request (thread 0 only)
+  auto request = [&](int g, int s) {
+    const int rows = n - g * RPI < RPI ? n - g * RPI : RPI;
+    const uint32_t bytes = static_cast<uint32_t>(rows) * row_bytes;
+    unsigned char* dst = buf + static_cast<uint32_t>(s) * stage_total;
+    const size_t off = static_cast<size_t>(g) * RPI * H;
+    mbar_expect_tx(&full[s], RES ? 2 * bytes : bytes);
+    bulk_load_1d(dst, xg + off, bytes, &full[s]);
+    if constexpr (RES) bulk_load_1d(dst + RPI * row_bytes, bg + off, bytes, &full[s]);
+  };
+  if (tid == 0) {
+    for (int s = 0; s < a.stages && pg < n_groups; ++s, ++pg) {
+      // test switch: CTA 0 never sends its first group, so the wait on stage 0 expires with nothing in flight
+      if (!(a.withhold_first_copy && blockIdx.x == 0 && s == 0)) request(pg, s);
+    }
+  }
+
+  // the sample's modulation vector, in registers
+  float2 sc[NP], sh[NP];
+  {
+    Vec<T, VEC> vs, vh;
+    vs.load(static_cast<const T*>(a.scale) + b * H + col);
+    vh.load(static_cast<const T*>(a.shift) + b * H + col);
+    unpack2<T, VEC>(vs, sc);
+    unpack2<T, VEC>(vh, sh);
+#pragma unroll
+    for (int i = 0; i < NP; ++i) sc[i] = __fadd2_rn(sc[i], make_float2(1.f, 1.f));
+  }
+  [[maybe_unused]] float2 gt[NP];
+  if constexpr (RES) {
+#pragma unroll
+    for (int i = 0; i < NP; ++i) gt[i] = make_float2(1.f, 1.f);
+    if (a.gate != nullptr) {
+      Vec<T, VEC> vg;
+      vg.load(static_cast<const T*>(a.gate) + b * H + col);
+      unpack2<T, VEC>(vg, gt);
+    }
+  }
+  T* yp = static_cast<T*>(a.y) + r0 * H + col;
+  [[maybe_unused]] T* xn = RES ? static_cast<T*>(a.dx) + r0 * H + col : nullptr;
+  float* mean_p = (!RMS && a.invstd != nullptr) ? a.mean + r0 : nullptr;
+  float* inv_p = a.invstd != nullptr ? a.invstd + r0 : nullptr;
+  const size_t group_elems = static_cast<size_t>(RPI) * H;
+  int stage = 0, phase = 0;
+  uint32_t parity = 0;
+
+  auto refill = [&]() {
+    if (tid == 0 && pg < n_groups) {  // every thread has read the stage: refill it
+      fence_proxy_async_smem();
+      request(pg, stage);
+      ++pg;
+    }
+  };
+
+  // one group of rows; FULL: all RPI rows exist (no row predicates). Returns false when the CTA must leave.
+  auto group = [&](auto full_tag, int nrows) -> bool {
+    constexpr bool FULL = decltype(full_tag)::value;
+    // A wait that expires raises the CTA's abort flag; everybody sees it after the next barrier (the one inside
+    // the row reduction) and the CTA leaves together.
+    if (!mbar_wait_1s(&full[stage], parity, a.err, 1, a.wait_limit_ns)) s_abort = 1;
+    // this thread's 16-byte column of each row (rows past the group's end hold stale data: they are reduced like
+    // the others, independently per row, and never stored)
+    const unsigned char* src =
+        active ? buf + static_cast<uint32_t>(stage) * stage_total + col * sizeof(T) : reinterpret_cast<const unsigned char*>(zero16);
+    float2 X[RPI][NP];
+#pragma unroll
+    for (int j = 0; j < RPI; ++j) {
+      Vec<T, VEC> pk;
+      *reinterpret_cast<uint4*>(pk.v) = *reinterpret_cast<const uint4*>(src + j * src_stride);
+      unpack2<T, VEC>(pk, X[j]);
+      if constexpr (RES) {
+        Vec<T, VEC> pb;
+        *reinterpret_cast<uint4*>(pb.v) = *reinterpret_cast<const uint4*>(src + br_off + j * src_stride);
+        float2 Bv[NP];
+        unpack2<T, VEC>(pb, Bv);
+#pragma unroll
+        for (int i = 0; i < NP; ++i) X[j][i] = __ffma2_rn(gt[i], Bv[i], X[j][i]);
+        pack2<T, VEC>(X[j], pk);  // the one rounding of the residual stream
+        if (active && (FULL || j < nrows)) pk.store(xn + static_cast<size_t>(j) * H);
+        unpack2<T, VEC>(pk, X[j]);  // the norm sees what was stored
+      }
+    }
+
+    float mean_mine[1] = {0.f};
+    if constexpr (!RMS) {
+      float s[1][RPI];
+#pragma unroll
+      for (int j = 0; j < RPI; ++j) {
+        float2 acc = X[j][0];
+#pragma unroll
+        for (int i = 1; i < NP; ++i) acc = __fadd2_rn(acc, X[j][i]);
+        s[0][j] = acc.x + acc.y;
+      }
+      cta_sum_rows_post<1, RPI>(s, mean_mine, red[phase], lane, warp, warps,
+                                [&](int, float t) { return -t * inv_h; });  // broadcast -mean
+      phase ^= 1;
+      if (*static_cast<volatile int*>(&s_abort)) return false;
+      refill();
+#pragma unroll
+      for (int j = 0; j < RPI; ++j) {
+        const float2 nm = make_float2(s[0][j], s[0][j]);
+#pragma unroll
+        for (int i = 0; i < NP; ++i) X[j][i] = __fadd2_rn(X[j][i], nm);  // deviations, in place
+      }
+    }
+
+    float q[1][RPI], rstd_mine[1];
+#pragma unroll
+    for (int j = 0; j < RPI; ++j) {
+      float2 acc = __fmul2_rn(X[j][0], X[j][0]);
+#pragma unroll
+      for (int i = 1; i < NP; ++i) acc = __ffma2_rn(X[j][i], X[j][i], acc);
+      q[0][j] = active ? acc.x + acc.y : 0.f;  // an idle lane's deviations are -mean, not 0
+    }
+    cta_sum_rows_post<1, RPI>(q, rstd_mine, red[phase], lane, warp, warps,
+                              [&](int, float t) { return rsqrt_newton(fmaf(t, inv_h, eps)); });  // broadcast 1/std
+    phase ^= 1;
+    if (*static_cast<volatile int*>(&s_abort)) return false;
+    if constexpr (RMS) refill();
+
+    if (tid < RPI && (FULL || tid < nrows) && inv_p != nullptr) {  // lane j of warp 0 owns row j's statistics
+      if constexpr (!RMS) mean_p[tid] = -mean_mine[0];
+      inv_p[tid] = rstd_mine[0];
+    }
+    if (active) {
+      T* out_p = yp;
+#pragma unroll
+      for (int j = 0; j < RPI; ++j) {
+        if (FULL || j < nrows) {
+          const float2 r2 = make_float2(q[0][j], q[0][j]);
+          float2 out[NP];
+#pragma unroll
+          for (int i = 0; i < NP; ++i) out[i] = __ffma2_rn(__fmul2_rn(X[j][i], r2), sc[i], sh[i]);
+          Vec<T, VEC> o;
+          pack2<T, VEC>(out, o);
+          o.store(out_p);
+        }
+        out_p += H;
+      }
+    }
+    if (++stage == a.stages) {
+      stage = 0;
+      parity ^= 1u;
+    }
+    yp += group_elems;
+    if constexpr (RES) xn += group_elems;
+    if (inv_p != nullptr) {
+      inv_p += RPI;
+      if constexpr (!RMS) mean_p += RPI;
+    }
+    return true;
+  };
+
+  const int n_full = n / RPI;
+  for (int g = 0; g < n_full; ++g) {
+    if (!group(std::true_type{}, RPI)) {
+      drain_after_abort();
+      return;
+    }
+  }
+  if (n_full < n_groups) {
+    if (!group(std::false_type{}, n - n_full * RPI)) {
+      drain_after_abort();
+      return;
+    }
+  }
+}
+
 // The fused backward (dx + column sums) for the launch plan that nearly every training shape gets: every chunk
 // lies inside one sample (`chunks_per_sample` > 0). Same pipeline, same arithmetic in the same order and the same
 // workspace slots as norm_bwd_tma<..., true, true> - results are bit-identical - but the walk is flat: the chunk
@@ -662,6 +875,13 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma_flat(const NormArgs a) {
       reinterpret_cast<float4*>(part + H)[kk] = make_float4(acc_h[2 * kk].x, acc_h[2 * kk].y, acc_h[2 * kk + 1].x, acc_h[2 * kk + 1].y);
     }
   }
+}
+
+template <typename T, int VEC, int RPI, int MAXRF, int MAXRB>
+static const void* pick_tma_flat_fwd(bool rms, bool res) {
+  if (res)
+    return rms ? (const void*)norm_fwd_tma_flat<T, VEC, RPI, MAXRB, true, true> : (const void*)norm_fwd_tma_flat<T, VEC, RPI, MAXRB, false, true>;
+  return rms ? (const void*)norm_fwd_tma_flat<T, VEC, RPI, MAXRF, true> : (const void*)norm_fwd_tma_flat<T, VEC, RPI, MAXRF, false>;
 }
 
 template <typename T, int VEC, int RPI, int MAXRB>
