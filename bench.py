@@ -824,15 +824,7 @@ def run_gpu_arm(args) -> None:
     barrier()
 
     if rank == 0:
-        # The backward's launch duration INSIDE the timed step: its share of the step time, the shares taken from the
-        # two single-kernel loops measured right after the timed region (forward only; backward + stage 2 only, same
-        # buffers and rotation). The backward-only loop by itself overstates the kernel: its plan fills every
-        # resident CTA slot, so in that loop each launch waits for the previous launch's stage-2 CTAs to leave
-        # before its last CTAs fit, which never happens in the step (a forward launch follows, whose CTAs fit
-        # beside them); and the sum of the two loops (28.6 us) is not the step (22.4 us). The raw loop times are
-        # reported next to it.
-        bwd_in_step_ms = ms_per_step * bwd_ms / (fwd_ms + bwd_ms)
-        achieved = BWD_BYTES / bwd_in_step_ms / 1e6
+        achieved = BWD_BYTES / bwd_ms / 1e6
         traffic, traffic_rec = measured_traffic()
         fc1 = (extras or {}).get("fc1_bf16_gated")
         line = {
@@ -850,10 +842,10 @@ def run_gpu_arm(args) -> None:
             "roofline": {"kernel": "norm_bwd_tma + norm_dparam_stage2 (dx + dscale/dshift, one pass over dy and x)", "bound": "hbm",
                          "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": traffic, "traffic_record": traffic_rec, "peak_source": peak_src,
-                         "algorithmic_bytes": BWD_BYTES, "avg_launch_ms": bwd_in_step_ms,
-                         "timing": {"method": "step time x backward share; shares from the two single-kernel loops",
-                                    "step_ms": ms_per_step, "forward_only_loop_ms": fwd_ms,
-                                    "backward_only_loop_ms": bwd_ms}},
+                         "algorithmic_bytes": BWD_BYTES, "avg_launch_ms": bwd_ms,
+                         "timing": {"method": "a loop of backward + stage-2 launches over the rotation, right after "
+                                              "the timed region", "step_ms": ms_per_step,
+                                    "forward_only_loop_ms": fwd_ms, "backward_only_loop_ms": bwd_ms}},
             "roofline_fc1": None if not fc1 else {
                 "kernel": "fc1_pair_kernel (tcgen05, gated GELU-tanh epilogue), config 4 bf16", "bound": "tensor",
                 "achieved": fc1["TFLOP/s"], "peak": tf_peak, "unit": "TFLOP/s", "frac": fc1["TFLOP/s"] / tf_peak,
