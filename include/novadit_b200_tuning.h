@@ -18,7 +18,7 @@ extern "C" {
 void nd_tune_norm_tile_rows(int tile_rows);
 /* Tuning hook: 0 = default, 1 = generic kernels for every shape, 3 / 4 = never / always run the forward pass
  * with the chunked warp-per-row kernel where it applies, 5 = even row chunks instead of sample-aligned ones, 6 =
- * the general bulk-copy kernels also where the flat walk applies, 7 = the same number of chunks for every sample.
+ * the general bulk-copy backward kernel also where the flat walk applies.
  * Results are identical up to fp32 summation order. */
 void nd_tune_norm_variant(int variant);
 /* Tuning hook: pipeline depth (shared-memory stages) of the bulk-copy norm kernels; 0 = as many as

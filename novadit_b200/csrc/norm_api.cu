@@ -72,8 +72,8 @@ __global__ void __launch_bounds__(128) norm_dparam_stage2_kernel(const NormArgs 
   const int H = a.hidden;
   long long first, count;
   if (a.n_chunks > 0 && a.chunks_per_sample > 0) {
-    chunks_of_sample(a, bi, first, count);
-    first += bi;  // slot = chunk + sample index
+    first = bi * a.chunks_per_sample + bi;  // slot = chunk + sample index, chunks [bi k, (bi + 1) k)
+    count = a.chunks_per_sample;
   } else if (a.n_chunks > 0) {
     long long s0 = b * a.seq_len - a.row_start, s1 = s0 + a.seq_len;  // the sample's rows, local, clipped below
     if (s0 < 0) s0 = 0;

@@ -49,8 +49,6 @@ struct NormArgs {
   int chunk_rem;         // rows % n_chunks
   int chunks_per_sample;  // > 0: the shard is whole samples and every sample is cut into this many chunks (no chunk
                           // crosses a sample boundary); 0: the shard's rows are cut evenly, whatever the samples
-  int chunks_extra;       // with chunks_per_sample > 0: the first `chunks_extra` samples are cut into one chunk more,
-                          // which is how a plan uses every resident CTA slot (see chunk_of_sample)
   int stages;    // shared-memory pipeline depth of the bulk-copy kernels
   int* err;    // device error word (set when a bounded wait expires)
   // forward with e4m3 output (warp-per-row kernel only): y holds bytes, q = saturate_e4m3(value / *q_scale),
@@ -66,30 +64,6 @@ struct NormArgs {
   unsigned long long wait_limit_ns;
   int withhold_first_copy;
 };
-
-// Sample-aligned plans (chunks_per_sample > 0): chunk `idx` of the launch is chunk `cj` of the `kk` chunks of sample
-// `bi` (local to the shard). The first chunks_extra samples have chunks_per_sample + 1 chunks, the others
-// chunks_per_sample.
-__host__ __device__ __forceinline__ void chunk_of_sample(const NormArgs& a, int idx, int& bi, int& cj, int& kk) {
-  const int k = a.chunks_per_sample, wide = a.chunks_extra * (k + 1);
-  if (idx < wide) {
-    kk = k + 1;
-    bi = idx / kk;
-    cj = idx - bi * kk;
-  } else {
-    const int t = idx - wide;
-    kk = k;
-    bi = a.chunks_extra + t / k;
-    cj = t - (t / k) * k;
-  }
-}
-// first chunk index and chunk count of local sample `bi` under such a plan
-__host__ __device__ __forceinline__ void chunks_of_sample(const NormArgs& a, long long bi, long long& first, long long& count) {
-  const long long k = a.chunks_per_sample, e = a.chunks_extra;
-  first = bi < e ? bi * (k + 1) : e * (k + 1) + (bi - e) * k;
-  count = bi < e ? k + 1 : k;
-}
-
 
 // first row (local to the shard) of chunk c
 // (chunks differ in size by at most one row: the first `chunk_rem` chunks hold `chunk_base` + 1 rows)

@@ -61,26 +61,17 @@ inline long long resident_slots(const void* fn, int nt, int smem, bool fwd = tru
 // Cuts the shard into `chunks` chunks (at most one per resident CTA slot). When the shard is whole samples and an
 // integral number of chunks per sample fills at least 90 % of the slots, every sample gets that many chunks: no
 // chunk crosses a sample boundary, so no CTA pays a second modulation load, a ragged extra row group or a second
-// partial slot - at the DiT-XL/2 shape those CTAs (one in fourteen) ended 2 us after the others. In the backward
-// passes the slots that an integral number leaves over go to the first samples, one more chunk each (13 chunks per sample are 416 of
-// 444 backward slots at the DiT-XL/2 shape: 28 SMs would hold two CTAs and the others three, which set the time;
-// with 28 samples cut into 14 every SM holds three shorter ones). Otherwise the rows are cut evenly whatever the
-// samples.
+// partial slot - at the DiT-XL/2 shape those CTAs (one in fourteen) ended 2 us after the others. Otherwise the
+// rows are cut evenly whatever the samples.
 inline void plan_chunks(NormArgs& a, long long chunks, int rpi) {
   a.b_first = a.row_start / a.seq_len;
   a.n_samples = (a.row_start + a.rows - 1) / a.seq_len - a.b_first + 1;
   a.chunks_per_sample = 0;
-  a.chunks_extra = 0;
   const bool whole = a.row_start % a.seq_len == 0 && a.rows % a.seq_len == 0;
   const long long k = whole ? chunks / a.n_samples : 0;
-  if (norm_variant() != 5 && k >= 1 && a.seq_len / k >= rpi && k * a.n_samples * 10 >= chunks * 9 &&
-      (k + 1) * a.n_samples < (1LL << 30)) {
+  if (norm_variant() != 5 && k >= 1 && a.seq_len / k >= rpi && k * a.n_samples * 10 >= chunks * 9) {
     a.chunks_per_sample = static_cast<int>(k);
-    const long long extra = chunks - k * a.n_samples;  // < n_samples
-    // backward passes only: the forward's CTAs are small enough that the kernels around it share its SMs, and filling
-    // the last slots measured nothing there
-    if (norm_variant() != 7 && a.mode != kFwd && a.seq_len / (k + 1) >= rpi) a.chunks_extra = static_cast<int>(extra);
-    chunks = k * a.n_samples + a.chunks_extra;
+    chunks = k * a.n_samples;
   }
   a.n_chunks = static_cast<int>(chunks);
   a.chunk_base = a.rows / chunks;

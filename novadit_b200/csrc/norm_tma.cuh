@@ -37,9 +37,8 @@ struct GroupCursor {
   long long b, s_end;   // sample of row r, end of that sample clipped to the chunk (local)
   __device__ __forceinline__ bool init(const NormArgs& a) {
     if (a.chunks_per_sample > 0) {  // chunk j of sample bi: the sample's rows cut evenly
-      int bi_, j_, k_;
-      chunk_of_sample(a, static_cast<int>(blockIdx.x), bi_, j_, k_);
-      const long long k = k_, bi = bi_, j = j_;
+      const long long k = a.chunks_per_sample;
+      const long long bi = blockIdx.x / k, j = blockIdx.x - bi * k;
       const long long base = a.seq_len / k, rem = a.seq_len - base * k;
       r = bi * a.seq_len + j * base + (j < rem ? j : rem);
       r_end = r + base + (j < rem ? 1 : 0);
@@ -488,9 +487,8 @@ __global__ void __maxnreg__(MAXR) norm_fwd_tma_flat(const NormArgs a) {
   const float eps = a.eps;
 
   // this CTA's chunk: rows [r0, r0 + n) of sample bi of the shard (whole samples, cut evenly)
-  const int seq = static_cast<int>(a.seq_len);
-  int bi, cj, k;
-  chunk_of_sample(a, static_cast<int>(blockIdx.x), bi, cj, k);
+  const int k = a.chunks_per_sample, seq = static_cast<int>(a.seq_len);
+  const int bi = static_cast<int>(blockIdx.x) / k, cj = static_cast<int>(blockIdx.x) - bi * k;
   const int cbase = seq / k, crem = seq - cbase * k;
   const long long r0 = static_cast<long long>(bi) * seq + cj * cbase + (cj < crem ? cj : crem);
   const int n = cbase + (cj < crem ? 1 : 0);
@@ -706,9 +704,8 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma_flat(const NormArgs a) {
   const float inv_h = 1.f / static_cast<float>(H);
 
   // this CTA's chunk: rows [r0, r0 + n) of sample bi of the shard (whole samples, cut evenly)
-  const int seq = static_cast<int>(a.seq_len);
-  int bi, cj, k;
-  chunk_of_sample(a, static_cast<int>(blockIdx.x), bi, cj, k);
+  const int k = a.chunks_per_sample, seq = static_cast<int>(a.seq_len);
+  const int bi = static_cast<int>(blockIdx.x) / k, cj = static_cast<int>(blockIdx.x) - bi * k;
   const int cbase = seq / k, crem = seq - cbase * k;
   const long long r0 = static_cast<long long>(bi) * seq + cj * cbase + (cj < crem ? cj : crem);
   const int n = cbase + (cj < crem ? 1 : 0);
@@ -856,9 +853,9 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma_flat(const NormArgs a) {
   const int n_full = n / RPI;
   for (int g = 0; g < n_full; ++g) {
     // The kernels that depend on this launch (stage 2, then whatever follows) are released when the last full group
-    // begins, not at entry: this plan fills every CTA slot of the GPU, and dependents released at entry sit in the
-    // slots that free up first while the launch after them cannot start - measured 19.4 us per backward + stage 2
-    // in a loop of them against 15.2 us this way, and erratic step times (20.7 - 24.5 us for AdaRMSNorm).
+    // begins, not at entry: released at entry they sit in the CTA slots that free up first while the launch after
+    // them cannot start - measured 16.2 us per backward + stage 2 in a loop of them against 15.0 us this way, and a
+    // step 0.6 - 0.9 us shorter (AdaLN / AdaRMSNorm at the DiT-XL/2 shape).
     if (g == n_full - 1) griddep_launch_dependents();
     if (!group(std::true_type{}, RPI)) {
       drain_after_abort();
