@@ -159,12 +159,11 @@ int launch_norm_tma(NormArgs a, cudaStream_t st) {
   const long long most = a.rows / RPI > 1 ? a.rows / RPI : 1;  // every chunk holds at least one full group
   if (chunks > most) chunks = most;
   plan_chunks(a, chunks, RPI);
-  // the forward and the fused backward of a plan whose chunks each lie inside one sample take the flat walk (same
-  // resources, same results bit for bit; variant 6 keeps the general kernels)
-  if ((a.mode == kBwdFused || a.mode == kFwd) && a.chunks_per_sample > 0 && a.seq_len < (1LL << 30) &&
-      norm_variant() != 6) {
+  // a plan whose chunks each lie inside one sample takes the flat walk in every mode (same resources, same results
+  // bit for bit; variant 6 keeps the general kernels)
+  if (a.chunks_per_sample > 0 && a.seq_len < (1LL << 30) && norm_variant() != 6) {
     const void* flat = a.mode == kFwd ? pick_tma_flat_fwd<T, VEC, RPI, 96, 128>(a.rms, a.res)
-                                      : pick_tma_flat_bwd<T, VEC, RPI, 128>(a.rms);
+                                      : pick_tma_flat_bwd<T, VEC, RPI, 128>(a.mode, a.rms);
     if (cudaFuncSetAttribute(flat, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess) fn = flat;
     else (void)cudaGetLastError();
   }

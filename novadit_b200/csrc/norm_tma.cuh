@@ -673,14 +673,14 @@ __global__ void __maxnreg__(MAXR) norm_fwd_tma_flat(const NormArgs a) {
   }
 }
 
-// The fused backward (dx + column sums) for the launch plan that nearly every training shape gets: every chunk
-// lies inside one sample (`chunks_per_sample` > 0). Same pipeline, same arithmetic in the same order and the same
-// workspace slots as norm_bwd_tma<..., true, true> - results are bit-identical - but the walk is flat: the chunk
+// The backward (dx, column sums, or both in one pass) for the launch plan that nearly every training shape gets:
+// every chunk lies inside one sample (`chunks_per_sample` > 0). Same pipeline, same arithmetic in the same order and
+// the same workspace slots as norm_bwd_tma - results are bit-identical - but the walk is flat: the chunk
 // is `n` rows of one sample, so there is no sample cursor, the modulation vector and the column accumulators are
 // set up once, row and byte positions are 32-bit offsets from bases computed once, and the groups of RPI rows
 // run through a body without row predicates; only a ragged last group takes the predicated body. At H = 1152 that
 // is about a sixth fewer instructions per row, and at this size time follows the instruction count.
-template <typename T, int VEC, int RPI, int MAXR, bool RMS>
+template <typename T, int VEC, int RPI, int MAXR, bool RMS, bool DX = true, bool DP = true>
 __global__ void __maxnreg__(MAXR) norm_bwd_tma_flat(const NormArgs a) {
   constexpr int NP = VEC / 2;
   constexpr int Q = RMS ? 1 : 2;  // row sums needed for dx: [sum dxhat,] sum dxhat*xhat
@@ -739,10 +739,10 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma_flat(const NormArgs a) {
     }
   }
 
-  float2 sc1[NP], acc_s[NP], acc_h[NP];
+  [[maybe_unused]] float2 sc1[NP], acc_s[NP], acc_h[NP];
 #pragma unroll
   for (int i = 0; i < NP; ++i) acc_s[i] = acc_h[i] = make_float2(0.f, 0.f);
-  {
+  if constexpr (DX) {
     Vec<T, VEC> vs;
     vs.load(static_cast<const T*>(a.scale) + b * H + col);
     unpack2<T, VEC>(vs, sc1);
@@ -751,7 +751,7 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma_flat(const NormArgs a) {
   }
   const float* inv_p = a.invstd + r0;
   const float* mean_p = RMS ? nullptr : a.mean + r0;
-  T* dp = static_cast<T*>(a.dx) + r0 * H + col;
+  [[maybe_unused]] T* dp = DX ? static_cast<T*>(a.dx) + r0 * H + col : nullptr;
   const size_t group_elems = static_cast<size_t>(RPI) * H;
   int stage = 0, phase = 0;
   uint32_t parity = 0;
@@ -800,19 +800,29 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma_flat(const NormArgs a) {
       for (int i = 0; i < NP; ++i) {
         if constexpr (!RMS) X[j][i] = __fadd2_rn(X[j][i], m2);
         X[j][i] = __fmul2_rn(X[j][i], r2);  // xhat in place
-        acc_h[i] = __fadd2_rn(acc_h[i], G[j][i]);
-        acc_s[i] = __ffma2_rn(G[j][i], X[j][i], acc_s[i]);
-        G[j][i] = __fmul2_rn(G[j][i], sc1[i]);  // dxhat in place
-        if constexpr (!RMS) p0 = __fadd2_rn(p0, G[j][i]);
-        p1 = __ffma2_rn(G[j][i], X[j][i], p1);
+        if constexpr (DP) {
+          acc_h[i] = __fadd2_rn(acc_h[i], G[j][i]);
+          acc_s[i] = __ffma2_rn(G[j][i], X[j][i], acc_s[i]);
+        }
+        if constexpr (DX) {
+          G[j][i] = __fmul2_rn(G[j][i], sc1[i]);  // dxhat in place
+          if constexpr (!RMS) p0 = __fadd2_rn(p0, G[j][i]);
+          p1 = __ffma2_rn(G[j][i], X[j][i], p1);
+        }
       }
-      if constexpr (!RMS) p[0][j] = p0.x + p0.y;
-      p[Q - 1][j] = p1.x + p1.y;
+      if constexpr (DX) {
+        if constexpr (!RMS) p[0][j] = p0.x + p0.y;
+        p[Q - 1][j] = p1.x + p1.y;
+      }
     }
-    float mine[Q];
-    cta_sum_rows_post<Q, RPI>(p, mine, red[phase], lane, warp, warps,
-                              [&](int, float t) { return -t * inv_h; });  // broadcast -mean_h(.)
-    phase ^= 1;
+    if constexpr (DX) {
+      float mine[Q];
+      cta_sum_rows_post<Q, RPI>(p, mine, red[phase], lane, warp, warps,
+                                [&](int, float t) { return -t * inv_h; });  // broadcast -mean_h(.)
+      phase ^= 1;
+    } else {
+      __syncthreads();  // every thread has read the stage
+    }
     if (*static_cast<volatile int*>(&s_abort)) return false;
     if (tid == 0 && pg < n_groups) {  // every thread has read the stage: refill it
       fence_proxy_async_smem();
@@ -823,7 +833,7 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma_flat(const NormArgs a) {
       stage = 0;
       parity ^= 1u;
     }
-    if (active) {
+    if (DX && active) {
       T* out_p = dp;
 #pragma unroll
       for (int j = 0; j < RPI; ++j) {
@@ -846,7 +856,7 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma_flat(const NormArgs a) {
     }
     inv_p += RPI;
     if constexpr (!RMS) mean_p += RPI;
-    dp += group_elems;
+    if constexpr (DX) dp += group_elems;
     return true;
   };
 
@@ -870,7 +880,7 @@ __global__ void __maxnreg__(MAXR) norm_bwd_tma_flat(const NormArgs a) {
   }
 
   // stage 1 of the dparam reduction: this chunk's column sums go to its own workspace slot
-  if (active) {
+  if (DP && active) {
     constexpr int NF4 = VEC / 4;  // float4 chunks per thread (VEC is 4 or 8)
     float* part = a.ws_part + (static_cast<long long>(blockIdx.x) + bi) * 2 * H + col;
 #pragma unroll
@@ -889,8 +899,17 @@ static const void* pick_tma_flat_fwd(bool rms, bool res) {
 }
 
 template <typename T, int VEC, int RPI, int MAXRB>
-static const void* pick_tma_flat_bwd(bool rms) {
-  return rms ? (const void*)norm_bwd_tma_flat<T, VEC, RPI, MAXRB, true> : (const void*)norm_bwd_tma_flat<T, VEC, RPI, MAXRB, false>;
+static const void* pick_tma_flat_bwd(int mode, bool rms) {
+  switch (mode) {
+    case kBwdDx:
+      return rms ? (const void*)norm_bwd_tma_flat<T, VEC, RPI, MAXRB, true, true, false>
+                 : (const void*)norm_bwd_tma_flat<T, VEC, RPI, MAXRB, false, true, false>;
+    case kBwdDparam:
+      return rms ? (const void*)norm_bwd_tma_flat<T, VEC, RPI, MAXRB, true, false, true>
+                 : (const void*)norm_bwd_tma_flat<T, VEC, RPI, MAXRB, false, false, true>;
+    default:
+      return rms ? (const void*)norm_bwd_tma_flat<T, VEC, RPI, MAXRB, true> : (const void*)norm_bwd_tma_flat<T, VEC, RPI, MAXRB, false>;
+  }
 }
 
 template <typename T, int VEC, int RPI, int MAXRF, int MAXRB>
