@@ -709,6 +709,11 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// A CTA of a pair that gives up (a bounded wait expired) raises the other CTA's abort flag too, so that the peer's
+// roles leave at their next poll instead of running into their own one-second limits one after the other.
+__device__ __forceinline__ void abort_peer(volatile int* my_flag, uint32_t peer_flag_cluster_addr) {
+  if (*my_flag) asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(peer_flag_cluster_addr), "r"(1) : "memory");
+}
 // 2-D tiled copy into this CTA's shared memory whose completion bytes are counted on an mbarrier that
 // may live in the other CTA of the pair (`bar_cluster_addr` is a shared::cluster address).
 __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0,
@@ -773,6 +778,7 @@ fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   cluster_sync_all();  // the peer's barriers exist before anything is signalled across the pair
   tc_fence_after();
   const uint32_t tmem_base = s.tmem_base;
+  const uint32_t peer_abort = mapa_u32(smem_u32(&s.abort_flag), rank ^ 1u);
   // Programmatic dependent launch: everything above (barriers, tensor memory, tensor-map prefetch) touches no global
   // memory and may run while the previous kernel in the stream drains; nothing below runs before that kernel has
   // completed and its writes are visible. A launch without the attribute passes both instructions at once.
@@ -812,6 +818,7 @@ fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 5), static_cast<unsigned long long>(clock64() - t_start));
         atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 7), global_ns() - ns_start);
       }
+      abort_peer(abort_flag, peer_abort);
       if (!ok) {
         const unsigned long long t0 = global_ns();
         while (global_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -825,6 +832,7 @@ fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       mma_issue_loop<F8, true, kPairStages, kPairStageBytes>(smem_u32(s.stage[0]), s.full, s.empty, s.tmem_full,
                                                               s.tmem_empty, tmem_base, umma_idesc_pair(ABF), my_tiles,
                                                               a.k_blocks, abort_flag, a.sink, 12, 13);
+      abort_peer(abort_flag, peer_abort);
     }
     __syncwarp();
   } else if (warp >= 2) {
@@ -853,7 +861,10 @@ fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
-    if (lane == 0) bulk_wait_all();
+    if (lane == 0) {
+      abort_peer(abort_flag, peer_abort);
+      bulk_wait_all();
+    }
   }
 
   tc_fence_before();
@@ -1325,6 +1336,7 @@ gemm_bwd_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   cluster_sync_all();  // the peer's barriers exist before anything is signalled across the pair
   tc_fence_after();
   const uint32_t tmem_base = s.tmem_base;
+  const uint32_t peer_abort = mapa_u32(smem_u32(&s.abort_flag), rank ^ 1u);
   // Programmatic dependent launch: everything above (barriers, tensor memory, tensor-map prefetch) touches no global
   // memory and may run while the previous kernel in the stream drains; nothing below runs before that kernel has
   // completed and its writes are visible. A launch without the attribute passes both instructions at once.
@@ -1363,6 +1375,7 @@ gemm_bwd_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           }
         }
       }
+      abort_peer(abort_flag, peer_abort);
       if (!ok) {  // let copies already issued land in shared memory before the CTA may exit
         const unsigned long long t0 = global_ns();
         while (global_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -1428,6 +1441,7 @@ gemm_bwd_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         }
         phase ^= 1u;
       }
+      abort_peer(abort_flag, peer_abort);
       if (a.trace != nullptr) {
         atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 5), static_cast<unsigned long long>(clock64() - t_start));
         atomicAdd(reinterpret_cast<unsigned long long*>(a.trace + 6), 1ull);
@@ -1539,7 +1553,10 @@ gemm_bwd_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
-    if (lane == 0) bulk_wait_all();
+    if (lane == 0) {
+      abort_peer(abort_flag, peer_abort);
+      bulk_wait_all();
+    }
   }
 
   tc_fence_before();
