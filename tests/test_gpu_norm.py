@@ -126,7 +126,7 @@ def test_inference_equals_training_output_bitwise(kind):
 
 
 @pytest.mark.parametrize("kind", ["layer", "rms"])
-@pytest.mark.parametrize("variant", [0, 1, 3, 4, 5])
+@pytest.mark.parametrize("variant", [0, 1, 3, 4, 5, 6])
 def test_every_kernel_variant_meets_the_bars(kind, variant):
     """The tuning knob selects among instantiations of the hot kernels; each must be correct."""
     x, scale, shift, dy = synth.norm_inputs(5, 77, 1152, torch.bfloat16, 8)
@@ -268,6 +268,36 @@ def test_dparam_does_not_depend_on_scratch_contents_or_replay(kind, mode, shape,
         assert torch.equal(ds[touched], want_ds[touched]) and torch.equal(dh[touched], want_dh[touched]), \
             f"graph replay {replay}"
     assert capi.lib().nd_device_error(0) == 0
+
+
+@pytest.mark.parametrize("kind", ["layer", "rms"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(32, 256, 1152), (3, 250, 768), (5, 77, 1536)])
+def test_the_flat_walk_agrees_with_the_general_kernels_bit_for_bit(kind, dtype, shape):
+    """Sample-aligned plans run the flat kernels (one sample per chunk, no row predicates in full groups); variant 6
+    keeps the general bulk-copy kernels. Same arithmetic in the same order: every output of the forward, of the
+    forward with the residual in front and of the three backward modes is bit-identical (ragged last groups and
+    chunk sizes that differ by one row included: 250 and 77 rows per sample)."""
+    x, scale, shift, dy = (t.to(DEV) for t in synth.norm_inputs(*shape, dtype, seed=5))
+    gate = (torch.arange(scale.numel(), device=DEV).reshape(scale.shape) % 7 * 0.125).to(dtype)
+    L = capi.lib()
+    outs = {}
+    try:
+        for variant in (6, 0):
+            L.nd_tune_norm_variant(variant)
+            f = capi.norm_fwd(kind, x, scale, shift, 1e-6)
+            mean, inv = (f[1], f[2]) if kind == "layer" else (None, f[1])
+            got = list(f) + list(capi.norm_fwd_residual(kind, x, dy, gate, scale, shift, 1e-6))
+            for mode in ("dx", "dparam", "fused"):
+                got += [t for t in capi.norm_bwd(kind, dy, x, scale, mean, inv, mode=mode) if t is not None]
+            outs[variant] = got
+    finally:
+        L.nd_tune_norm_variant(0)
+    torch.cuda.synchronize()
+    assert len(outs[0]) == len(outs[6])
+    for a, b in zip(outs[0], outs[6]):
+        assert torch.equal(a, b)
+    assert L.nd_device_error(0) == 0
 
 
 def test_dparam_is_deterministic_run_to_run():
