@@ -410,7 +410,7 @@ __device__ __forceinline__ void epilogue_columns_bwd(const Fc1Args& a, const CUt
         dv[j] = rv.x; dv[j + 1] = rv.y;
       }
       const float sg = warp_colsum32(dg, lane), sv = warp_colsum32(dv, lane);
-      if (col + lane < a.n_out) {
+      if (col + lane < a.n_out && (row0 >> 5) < a.tiles_m * 4) {  // (a pair tile may reach past the last 128-row tile)
         float* row = a.dbias_part + static_cast<size_t>(row0 >> 5) * a.n;
         row[col + lane] = sg;
         row[a.n_out + col + lane] = sv;
@@ -670,17 +670,24 @@ fc1_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CU
 constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = kATileBytes + kBHalfBytes;  // 32 KB per CTA and stage
 
-struct __align__(1024) Fc1PairSmem {
-  uint8_t stage[kPairStages][kPairStageBytes];
-  uint8_t out[kEpilogueWarps][kOutBlockBytes];
+constexpr int kPairBwdStages = 5;  // the backward-dz variant trades one operand stage for two more epilogue blocks
+
+// STAGES operand stages; BLOCKS 32 x 32 staging blocks per epilogue warp (1: output; 3: dy in, two dz halves out)
+template <int STAGES, int BLOCKS>
+struct __align__(1024) Fc1PairSmemT {
+  uint8_t stage[STAGES][kPairStageBytes];
+  uint8_t out[kEpilogueWarps][BLOCKS][kOutBlockBytes];
   alignas(16) float bias[kEpilogueWarps][kBN];
-  uint64_t full[kPairStages];    // used in the leader only: bytes of both CTAs land here
-  uint64_t empty[kPairStages];   // in each CTA: signalled by the leader's commit
+  uint64_t full[STAGES];         // used in the leader only: bytes of both CTAs land here
+  uint64_t empty[STAGES];        // in each CTA: signalled by the leader's commit
   uint64_t tmem_full[2];         // in each CTA: signalled by the leader's commit
   uint64_t tmem_empty[2];        // used in the leader only: the epilogue warps of both CTAs arrive here
+  uint64_t dy_full[kEpilogueWarps];  // backward: the warp's dy block has landed
   uint32_t tmem_base;
   int abort_flag;
 };
+using Fc1PairSmem = Fc1PairSmemT<kPairStages, 1>;
+using Fc1PairBwdSmem = Fc1PairSmemT<kPairBwdStages, 3>;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -739,12 +746,18 @@ __device__ __forceinline__ void pair_tile_coords(int tiles_m2, int tiles_n, int 
   ni = r / gm;
 }
 
-template <bool F8, int ABF, int GATED, int ACT, typename OUT>
+// BWD: the epilogue is the activation backward, as in fc1_kernel (map_y / map_y2 the two halves of dz, map_dy the
+// incoming gradient)
+template <bool F8, int ABF, int GATED, int ACT, typename OUT, bool BWD = false>
 __global__ void __launch_bounds__(kThreads, 1)
 fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                const __grid_constant__ CUtensorMap map_y, const Fc1Args a) {
+                const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_y2,
+                const __grid_constant__ CUtensorMap map_dy, const Fc1Args a) {
+  static_assert(!BWD || (GATED == 1 && !F8), "the backward epilogue exists for stacked gating and 16-bit operands");
+  constexpr int kS = BWD ? kPairBwdStages : kPairStages;
+  using Smem = Fc1PairSmemT<kS, BWD ? 3 : 1>;
   extern __shared__ uint8_t smem_raw[];
-  Fc1PairSmem& s = *reinterpret_cast<Fc1PairSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &s.abort_flag;
   constexpr int kBKElems = F8 ? 128 : 64;
@@ -754,10 +767,11 @@ fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   const int first_tile = static_cast<int>(cluster_id_x()), tile_step = static_cast<int>(cluster_count_x());
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kPairStages; ++i) {
+    for (int i = 0; i < kS; ++i) {
       mbar_init(&s.full[i], 1);
       mbar_init(&s.empty[i], 1);
     }
+    for (int i = 0; i < kEpilogueWarps; ++i) mbar_init(&s.dy_full[i], 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.tmem_full[i], 1);
       mbar_init(&s.tmem_empty[i], 2 * kEpilogueWarps);
@@ -808,7 +822,7 @@ fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           uint8_t* base = s.stage[stage];
           tma_load_2d_pair(base, &map_x, leader_full, kb * kBKElems, m0);
           tma_load_2d_pair(base + kATileBytes, &map_w, leader_full, kb * kBKElems, nb);
-          if (++stage == kPairStages) {
+          if (++stage == kS) {
             stage = 0;
             phase ^= 1u;
           }
@@ -829,7 +843,7 @@ fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     // ---------------------------------------------------------------- MMA issuer (one thread of the leader)
     if (lane == 0) {
       const int my_tiles = first_tile < total_tiles ? (total_tiles - 1 - first_tile) / tile_step + 1 : 0;
-      mma_issue_loop<F8, true, kPairStages, kPairStageBytes>(smem_u32(s.stage[0]), s.full, s.empty, s.tmem_full,
+      mma_issue_loop<F8, true, kS, kPairStageBytes>(smem_u32(s.stage[0]), s.full, s.empty, s.tmem_full,
                                                               s.tmem_empty, tmem_base, umma_idesc_pair(ABF), my_tiles,
                                                               a.k_blocks, abort_flag, a.sink, 12, 13);
       abort_peer(abort_flag, peer_abort);
@@ -841,6 +855,7 @@ fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     const int colhalf = (warp - 2) >> 2;
     int acc = 0;
     uint32_t acc_phase = 0;
+    [[maybe_unused]] uint32_t dy_phase = 0;
     float alpha = a.alpha_host;
     if (a.alpha_dev != nullptr) alpha *= __ldg(a.alpha_dev) * __ldg(a.alpha_dev + 1);
     bool ok = true;
@@ -854,7 +869,13 @@ fc1_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       tc_fence_after();
       const int row0 = mi * 2 * kBM + static_cast<int>(rank) * kBM + q * 32;
       const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * kBN);
-      epilogue_columns<GATED, ACT, OUT, F8>(a, &map_y, sb, s.out[warp - 2], t_lane, row0, ni, colhalf, alpha, lane);
+      if constexpr (BWD) {
+        epilogue_columns_bwd<ACT, OUT>(a, &map_dy, &map_y, &map_y2, sb, s.out[warp - 2][0], &s.dy_full[warp - 2], dy_phase,
+                                       abort_flag, t_lane, row0, ni, colhalf, alpha, lane, ok);
+        if (!ok) break;
+      } else {
+        epilogue_columns<GATED, ACT, OUT, F8>(a, &map_y, sb, s.out[warp - 2][0], t_lane, row0, ni, colhalf, alpha, lane);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&s.tmem_empty[acc]), 0));  // the leader counts both CTAs
@@ -1731,9 +1752,7 @@ extern "C" int nd_fc1_fwd(int ab_dtype, int out_dtype, int act, int gated, const
     (void)cudaGetLastError();
     return ND_ERR_LAUNCH;
   }
-  void* params_single[] = {&map_x, &map_w, &map_y, &map_y, &map_y, &a};  // the forward epilogue uses the first of these only
-  void* params_pair[] = {&map_x, &map_w, &map_y, &a};
-  void** params = pair ? params_pair : params_single;
+  void* params[] = {&map_x, &map_w, &map_y, &map_y, &map_y, &a};  // the forward epilogue uses the first output map only
   cudaLaunchConfig_t cfg{};
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem_bytes;
@@ -1828,6 +1847,7 @@ static int fc1_bwd_dz_impl(int dtype, int act, const void* x, const void* w, con
 
   Fc1Args a{};
   a.dbias_part = dbias != nullptr ? static_cast<float*>(ws) : nullptr;
+  a.trace = g_fc1_trace.load(std::memory_order_relaxed);
   a.bias = bias; a.y = dz; a.sink = Fc1Sink{status, device_error_ptr()}; a.alpha_host = 1.f;
   a.m = static_cast<int>(m); a.k = static_cast<int>(k); a.n = static_cast<int>(n);
   a.n_out = static_cast<int>(n_out);
@@ -1856,14 +1876,25 @@ static int fc1_bwd_dz_impl(int dtype, int act, const void* x, const void* w, con
   if (!block_map(&map_dzg, dzb, n_out, n) || !block_map(&map_dzv, dzb + n_out * 2, n_out, n) ||
       !block_map(&map_dy, dy, n_out, n_out))
     return ND_ERR_LAUNCH;
+  // CTA-pair tiles as in the forward pass: once there are at least two rounds of single-CTA tiles
+  const int pair_mode = g_fc1_pair.load(std::memory_order_relaxed);
+  const bool pair = pair_mode >= 0 ? pair_mode != 0 : tiles >= 2LL * sm_count();
   const void* fn;
-  if (dtype == ND_BF16)
+  if (pair) {
+    if (dtype == ND_BF16)
+      fn = act == ND_ACT_SILU ? (const void*)fc1_pair_kernel<false, 1, 1, ND_ACT_SILU, __nv_bfloat16, true>
+                              : (const void*)fc1_pair_kernel<false, 1, 1, ND_ACT_GELU, __nv_bfloat16, true>;
+    else
+      fn = act == ND_ACT_SILU ? (const void*)fc1_pair_kernel<false, 0, 1, ND_ACT_SILU, __half, true>
+                              : (const void*)fc1_pair_kernel<false, 0, 1, ND_ACT_GELU, __half, true>;
+  } else if (dtype == ND_BF16) {
     fn = act == ND_ACT_SILU ? (const void*)fc1_kernel<false, 1, 1, ND_ACT_SILU, __nv_bfloat16, true>
                             : (const void*)fc1_kernel<false, 1, 1, ND_ACT_GELU, __nv_bfloat16, true>;
-  else
+  } else {
     fn = act == ND_ACT_SILU ? (const void*)fc1_kernel<false, 0, 1, ND_ACT_SILU, __half, true>
                             : (const void*)fc1_kernel<false, 0, 1, ND_ACT_GELU, __half, true>;
-  const int smem_bytes = static_cast<int>(sizeof(Fc1BwdSmem)) + 1024;
+  }
+  const int smem_bytes = static_cast<int>(pair ? sizeof(Fc1PairBwdSmem) : sizeof(Fc1BwdSmem)) + 1024;
   cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) {
     set_last_cuda_error(e);
@@ -1878,11 +1909,27 @@ static int fc1_bwd_dz_impl(int dtype, int act, const void* x, const void* w, con
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr{};
-    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr.val.programmaticStreamSerializationAllowed = g_fc1_pdl.load(std::memory_order_relaxed) != 0 ? 1 : 0;
-    cfg.attrs = &attr;
+    cudaLaunchAttribute attrs[2] = {};
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = g_fc1_pdl.load(std::memory_order_relaxed) != 0 ? 1 : 0;
+    cfg.attrs = attrs;
     cfg.numAttrs = 1;
+    if (pair) {  // persistent grid of CTA pairs, as in nd_fc1_fwd
+      attrs[1].id = cudaLaunchAttributeClusterDimension;
+      attrs[1].val.clusterDim.x = 2;
+      attrs[1].val.clusterDim.y = 1;
+      attrs[1].val.clusterDim.z = 1;
+      cfg.numAttrs = 2;
+      const long long pair_tiles = static_cast<long long>((a.m + 2 * kBM - 1) / (2 * kBM)) * a.tiles_n;
+      cfg.gridDim = dim3(static_cast<unsigned>(2 * (sm_count() / 2)));
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, fn, &cfg) != cudaSuccess || clusters < 1) {
+        (void)cudaGetLastError();
+        clusters = sm_count() / 2;
+      }
+      if (clusters > pair_tiles) clusters = static_cast<int>(pair_tiles);
+      cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+    }
     e = cudaLaunchKernelExC(&cfg, fn, params);
   }
   if (e != cudaSuccess) {

@@ -82,8 +82,11 @@ def test_identity_epilogue_is_a_plain_gemm(dtype, mkn, bias):
     (torch.bfloat16, (1, 64, 16), True),
     (torch.bfloat16, (2048, 1152, 9216), True),   # DiT-XL/2 MLP width, several tiles per CTA
 ])
-def test_backward_dz_kernel_matches_oracle(act, dtype, mkn, bias):
-    """dz = d(value * act(gate)) / dz with z recomputed inside the kernel, against the fp64 closed form."""
+@pytest.mark.parametrize("pair", [0, 1])
+def test_backward_dz_kernel_matches_oracle(tile_mode, pair, act, dtype, mkn, bias):
+    """dz = d(value * act(gate)) / dz with z recomputed inside the kernel, against the fp64 closed form; on single-CTA
+    tiles and on CTA-pair tiles."""
+    tile_mode(pair)
     m, k, n = mkn
     x, w, b = synth.fc1_inputs(m, k, n, dtype, seed=71)
     dy = torch.randn(m, n // 2, generator=torch.Generator().manual_seed(72)).to(dtype)
@@ -105,8 +108,11 @@ def test_backward_dz_kernel_matches_oracle(act, dtype, mkn, bias):
     (torch.bfloat16, (1, 64, 16)),
     (torch.bfloat16, (2048, 1152, 9216)),  # DiT-XL/2 MLP width: 16 row tiles x 4 quarters of partial sums
 ])
-def test_backward_dz_with_dbias_in_the_epilogue(act, dtype, mkn):
-    """nd_fc1_bwd_dz_dbias: the same dz bit for bit, and dbias = the fp32 sum over the tokens of the STORED dz."""
+@pytest.mark.parametrize("pair", [0, 1])
+def test_backward_dz_with_dbias_in_the_epilogue(tile_mode, pair, act, dtype, mkn):
+    """nd_fc1_bwd_dz_dbias: the same dz bit for bit, and dbias = the fp32 sum over the tokens of the STORED dz; on
+    single-CTA tiles and on CTA-pair tiles (whose second CTA may lie wholly past the last row)."""
+    tile_mode(pair)
     m, k, n = mkn
     x, w, b = synth.fc1_inputs(m, k, n, dtype, seed=73)
     dy = torch.randn(m, n // 2, generator=torch.Generator().manual_seed(74)).to(dtype)
